@@ -16,7 +16,7 @@ import torch
 from . import models  # noqa: F401  (registers the architectures)
 from .config.errors import UnsupportedDType
 from .config.generation import GenerationConfig, load_generation_config
-from .config.metadata import canonical_dtype, metadata_from_json, read_config_json, validate_run_dtype
+from .config.metadata import ModelMetadata, canonical_dtype, metadata_from_json, read_config_json, validate_run_dtype
 from .config.registry import architecture_for
 from .engine.generate import GenerationMetrics, GenerationResult, generate_tokens
 from .engine.step import Engine
@@ -52,6 +52,8 @@ def load_model(folder: str, dtype: str = "auto", device="gpu", enforce_declared_
     raw = read_config_json(folder)
     metadata = metadata_from_json(raw)
     entry = architecture_for(raw)
+    if metadata.declared_dtype is None and entry.storage_dtype is not None:
+        metadata = ModelMetadata(metadata.architecture, metadata.model_type, entry.storage_dtype)
     run_dtype = resolve_dtype(dtype, metadata.declared_dtype)
     if enforce_declared_dtype:
         run_dtype = validate_run_dtype(metadata, run_dtype)

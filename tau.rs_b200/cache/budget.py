@@ -38,6 +38,8 @@ def kv_bytes_per_token(groups: Dict[str, Tuple[object, int]], element_bytes: int
     for need, layers in groups.values():
         if need.kind == "kv":
             total += 2 * layers * need.n_kv_heads * need.head_dim * element_bytes
+        elif need.kind == "rows":
+            total += layers * need.row_width * element_bytes
     return total
 
 

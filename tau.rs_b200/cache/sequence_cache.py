@@ -10,7 +10,8 @@ back, and the capacity axis becomes pages of `PAGE_TOKENS` positions that a sequ
 takes as it grows, so that the cache is sized by the tokens that live sequences hold
 together and not by the longest of them times their number.
 
-A group is a set of cache layers with the same need (`CacheNeed`): a `kv` group has one
+A group is a set of cache layers with the same need (`CacheNeed`): a `kv` group (and a `rows` group, which keeps one
+row per position in one pool `[cache layers, pages, PAGE_TOKENS, row_width]` instead of keys and values) has one
 pool of pages for keys and one for values, `[cache layers, pages, kv heads, PAGE_TOKENS,
 head_dim]`, and on the host a page table `[slots, pages per sequence]`; a page number
 means the same page in every layer of the group.  Each step carries the table rows of
@@ -53,6 +54,13 @@ class KVLayerView:
 
 
 @dataclass
+class RowsLayerView:
+    rows: torch.Tensor        # [pages, PAGE_TOKENS, row_width]
+    group: str
+    window: Optional[int]
+
+
+@dataclass
 class StateLayerView:
     state: torch.Tensor       # [slots, *shape]
 
@@ -60,9 +68,13 @@ class StateLayerView:
 class _KVGroup:
     def __init__(self, need: CacheNeed, layers: int, pages: int, slots: int, pages_per_sequence: int, dtype, device):
         self.need, self.layers = need, layers
-        shape = (layers, pages, need.n_kv_heads, PAGE_TOKENS, need.head_dim)
-        self.keys = torch.empty(shape, dtype=dtype, device=device)
-        self.values = torch.empty(shape, dtype=dtype, device=device)
+        if need.kind == "rows":     # one row per position: the pages of a kv group without heads, and nothing beside them
+            self.keys = torch.empty((layers, pages, PAGE_TOKENS, need.row_width), dtype=dtype, device=device)
+            self.values = None
+        else:
+            shape = (layers, pages, need.n_kv_heads, PAGE_TOKENS, need.head_dim)
+            self.keys = torch.empty(shape, dtype=dtype, device=device)
+            self.values = torch.empty(shape, dtype=dtype, device=device)
         self.pool = FreeList(pages, "cache page")
         self.table = np.zeros((slots, pages_per_sequence), dtype=np.int32)
         self.held: Dict[int, List[int]] = {}          # the pages a sequence holds, oldest first
@@ -72,6 +84,8 @@ class _KVGroup:
         return min(length, self.need.window) if self.need.window else length
 
     def bytes_per_token(self) -> int:
+        if self.need.kind == "rows":
+            return self.layers * self.need.row_width * self.keys.element_size()
         return 2 * self.layers * self.need.n_kv_heads * self.need.head_dim * self.keys.element_size()
 
 
@@ -96,7 +110,7 @@ class SequenceCache:
         self.n_pages = pages_for(max_tokens)
         # A sequence cannot hold more pages than there are, unless every kv group lets old pages go (a window) or the model
         # keeps no keys and values at all (state of fixed size only).
-        kv_needs = [need for need, _ in groups.values() if need.kind == "kv"]
+        kv_needs = [need for need, _ in groups.values() if need.kind in ("kv", "rows")]
         bounded = all(need.window for need in kv_needs)
         self.widest_window = max((need.window for need in kv_needs), default=0) if bounded else None
         self.pages_per_sequence = pages_for(max_sequence_tokens) if bounded else min(self.n_pages, pages_for(max_sequence_tokens))
@@ -107,7 +121,7 @@ class SequenceCache:
         self.kv: Dict[str, _KVGroup] = {}
         self.states: Dict[str, _StateGroup] = {}
         for name, (need, layers) in groups.items():
-            if need.kind == "kv":
+            if need.kind in ("kv", "rows"):
                 self.kv[name] = _KVGroup(need, layers, self.n_pages, self.n_slots, self.pages_per_sequence, dtype, device)
             elif need.kind == "state":
                 self.states[name] = _StateGroup(need, layers, self.n_slots, device)
@@ -190,6 +204,8 @@ class SequenceCache:
     def layer_view(self, group: str, layer: int):
         if group in self.kv:
             entry = self.kv[group]
+            if entry.need.kind == "rows":
+                return RowsLayerView(entry.keys[layer], group, entry.need.window)
             return KVLayerView(entry.keys[layer], entry.values[layer], group, entry.need.window)
         return StateLayerView(self.states[group].state[layer])
 

@@ -4,4 +4,6 @@ from .metadata import (ModelMetadata, canonical_dtype, metadata_from_json, read_
 from .qwen3 import Qwen3Config
 from .registry import (Architecture, architecture_for, register_architecture, registered_architectures,
                        spec_from_config_json, unregister_architecture)
-from .specs import (AttentionSpec, BlockSpec, ModelSpec, NormSpec, PositionSpec, ScheduleEntry, SwiGLUSpec)
+from .fasesun import FasesunConfig
+from .specs import (AttentionSpec, BlockSpec, LatentAttentionSpec, LinearRecurrenceSpec, ModelSpec, NormSpec, PairRotationSpec,
+                    PositionSpec, RoutedExpertsSpec, ScheduleEntry, SwiGLUSpec)

@@ -59,6 +59,10 @@ def read_config_json(folder: str) -> dict:
 
 def metadata_from_json(raw: dict) -> ModelMetadata:
     architectures = raw.get("architectures")
+    if architectures is None and isinstance(raw.get("architecture"), str):
+        # The short spelling: one name under `architecture`, which is the model type as well unless that is given.
+        architectures = [raw["architecture"]]
+        raw = {"model_type": raw["architecture"].lower(), **raw}
     if not isinstance(architectures, list) or not architectures or not isinstance(architectures[0], str):
         raise InvalidConfig("config.json must name the model class in architectures[0]")
     model_type = raw.get("model_type")

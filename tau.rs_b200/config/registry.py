@@ -9,7 +9,7 @@ model itself is always built from the spec by `tau_rs_b200.parts.model.DecoderMo
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Callable, Dict
+from typing import Callable, Dict, Optional
 
 from .errors import InvalidConfig
 from .metadata import metadata_from_json
@@ -22,13 +22,15 @@ class Architecture:
     model_type: str
     parse_config: Callable[[dict], object]
     build_spec: Callable[[object], ModelSpec]
+    # The dtype that a folder of this architecture holds when its config.json declares none (None: float32 alone runs then).
+    storage_dtype: Optional[str] = None
 
 
 _ARCHITECTURES: Dict[str, Architecture] = {}
 
 
-def register_architecture(name: str, model_type: str, parse_config, build_spec) -> Architecture:
-    entry = Architecture(name, model_type, parse_config, build_spec)
+def register_architecture(name: str, model_type: str, parse_config, build_spec, storage_dtype: Optional[str] = None) -> Architecture:
+    entry = Architecture(name, model_type, parse_config, build_spec, storage_dtype)
     _ARCHITECTURES[name] = entry
     return entry
 

@@ -16,9 +16,13 @@ template <typename TIn, typename TOut>
 __global__ void __launch_bounds__(kThreads)
 gemm_simt_kernel(const TIn* __restrict__ x, const TIn* __restrict__ w, const float* __restrict__ bias,
                  TOut* __restrict__ out, int M, int N, int K, long long x_stride, long long w_stride,
-                 long long out_stride) {
+                 long long out_stride, long long x_batch, long long w_batch, long long out_batch) {
     grid_dependents_launch();
     grid_dependency_wait();
+    // blockIdx.z numbers the products of a batch (one per head, say); each has its operands a fixed distance further on.
+    x += blockIdx.z * x_batch;
+    w += blockIdx.z * w_batch;
+    out += blockIdx.z * out_batch;
     __shared__ float xs[kDepth][kTile + 4];
     __shared__ float ws[kDepth][kTile + 4];
     const int row0 = blockIdx.y * kTile, col0 = blockIdx.x * kTile;
@@ -66,10 +70,11 @@ gemm_simt_kernel(const TIn* __restrict__ x, const TIn* __restrict__ w, const flo
 
 template <typename TIn, typename TOut>
 int launch(const void* x, const void* w, const float* bias, void* out, int M, int N, int K, long long x_stride,
-           long long w_stride, long long out_stride, cudaStream_t stream) {
-    dim3 grid((N + kTile - 1) / kTile, (M + kTile - 1) / kTile);
+           long long w_stride, long long out_stride, cudaStream_t stream, int batch = 1, long long x_batch = 0, long long w_batch = 0,
+           long long out_batch = 0) {
+    dim3 grid((N + kTile - 1) / kTile, (M + kTile - 1) / kTile, batch);
     tau_launch(gemm_simt_kernel<TIn, TOut>, dim3(grid), dim3(kThreads), 0, stream, static_cast<const TIn*>(x), static_cast<const TIn*>(w), bias,
-                                                              static_cast<TOut*>(out), M, N, K, x_stride, w_stride, out_stride);
+                                                              static_cast<TOut*>(out), M, N, K, x_stride, w_stride, out_stride, x_batch, w_batch, out_batch);
     return tau_launch_status();
 }
 
@@ -84,5 +89,19 @@ TAU_EXPORT int tau_gemm_simt(int in_dtype, int out_dtype, const void* x, const v
     if (in_dtype == TAU_F32 && out_dtype == TAU_F32) return launch<float, float>(x, w, bias, out, M, N, K, x_stride, w_stride, out_stride, s);
     if (in_dtype == TAU_BF16 && out_dtype == TAU_BF16) return launch<bf16, bf16>(x, w, bias, out, M, N, K, x_stride, w_stride, out_stride, s);
     if (in_dtype == TAU_BF16 && out_dtype == TAU_F32) return launch<bf16, float>(x, w, bias, out, M, N, K, x_stride, w_stride, out_stride, s);
+    return cudaErrorInvalidValue;
+}
+
+// `batch` products of the same sizes in one launch: product b reads x + b * x_batch and w + b * w_batch and writes out + b * out_batch
+// (elements).  No bias.
+TAU_EXPORT int tau_gemm_simt_batched(int in_dtype, int out_dtype, const void* x, const void* w, void* out, int M, int N, int K, long long x_stride,
+                                     long long w_stride, long long out_stride, int batch, long long x_batch, long long w_batch, long long out_batch,
+                                     void* stream) {
+    if (M <= 0 || N <= 0 || batch <= 0) return 0;
+    if (!x || !w || !out || K <= 0 || batch > 65535) return cudaErrorInvalidValue;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (in_dtype == TAU_F32 && out_dtype == TAU_F32) return launch<float, float>(x, w, nullptr, out, M, N, K, x_stride, w_stride, out_stride, s, batch, x_batch, w_batch, out_batch);
+    if (in_dtype == TAU_BF16 && out_dtype == TAU_BF16) return launch<bf16, bf16>(x, w, nullptr, out, M, N, K, x_stride, w_stride, out_stride, s, batch, x_batch, w_batch, out_batch);
+    if (in_dtype == TAU_BF16 && out_dtype == TAU_F32) return launch<bf16, float>(x, w, nullptr, out, M, N, K, x_stride, w_stride, out_stride, s, batch, x_batch, w_batch, out_batch);
     return cudaErrorInvalidValue;
 }

@@ -82,6 +82,8 @@ _CLASS_OF = {
     "gemm_skinny": "product", "gemm_tc": "product", "attention_prepare": "attention", "attention": "attention",
     "attention_decode": "attention", "attention_prefill": "attention", "attention_prefill_tc": "attention", "argmax": "selection",
     "sample_gumbel": "selection", "store_words_host": "selection", "random_normal": "other",
+    "stream_add_norm": "norm", "gated_group_norm": "norm", "gemm_simt_batched": "product", "linear_recurrence": "recurrence",
+    "latent_prepare": "attention", "latent_attention": "attention", "moe_route": "routing", "moe_gate_up": "product", "moe_down": "product",
 }
 _timing = None     # while timing: [last event, [(class, event after the launch), ...]]
 
@@ -142,15 +144,25 @@ def _int_vector(tensor: torch.Tensor, what: str) -> None:
 def embedding(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> None:
     _on_device(tokens, table, out)
     _int_vector(tokens, "token ids")
-    _require(table.dtype == out.dtype and table.is_contiguous() and out.is_contiguous(), "table and output must match")
     _require(out.shape == (tokens.shape[0], table.shape[1]), "output must be [tokens, width]")
+    if out.dtype == torch.float32 and table.dtype != torch.float32:   # rows widened into a 32-bit residual stream
+        _require(table.is_contiguous() and out.is_contiguous(), "table and output must be contiguous")
+        library = build.load_library("stream32.cu")
+        return _check(library.tau_embedding_f32(_code(table), _pointer(tokens), _pointer(table), _pointer(out), ctypes.c_int(tokens.shape[0]),
+                                                ctypes.c_int(table.shape[1]), ctypes.c_int(table.shape[0]), _stream()), "embedding")
+    _require(table.dtype == out.dtype and table.is_contiguous() and out.is_contiguous(), "table and output must match")
     library = build.load_library("elementwise.cu")
     _check(library.tau_embedding(_code(table), _pointer(tokens), _pointer(table), _pointer(out), ctypes.c_int(tokens.shape[0]),
                                  ctypes.c_int(table.shape[1]), ctypes.c_int(table.shape[0]), _stream()), "embedding")
 
 
 def rms_norm(values, weight, eps: float, out, rows=None, branch=None) -> None:
-    """`out[i] = norm(round(values[r] + branch[r])) * weight`, `r = rows[i]` or `i`; `values` is not changed."""
+    """`out[i] = norm(round(values[r] + branch[r])) * weight`, `r = rows[i]` or `i`; `values` is not changed.
+
+    Where `values` is a 32-bit stream and the output is not, or there are two branches (a tuple), the sum is taken in
+    32-bit (`values[r] + (a[r] + b[r])`) and only the output is rounded."""
+    if isinstance(branch, (tuple, list)) or values.dtype != out.dtype:
+        return stream_add_norm(values, branch, weight, eps, out, rows=rows, update=False)
     _on_device(values, weight, out, rows, branch)
     width = values.shape[-1]
     _f32_vector(weight, width, "the norm weight")
@@ -168,7 +180,10 @@ def rms_norm(values, weight, eps: float, out, rows=None, branch=None) -> None:
 
 
 def add_rms_norm(branch, residual, weight, eps: float, out) -> None:
-    """`residual = round(residual + branch)` in place; `out = norm(residual) * weight`."""
+    """`residual = round(residual + branch)` in place; `out = norm(residual) * weight`.  A 32-bit residual beside an output
+    of another dtype, or two branches (a tuple), go to `stream_add_norm`."""
+    if isinstance(branch, (tuple, list)) or residual.dtype != out.dtype:
+        return stream_add_norm(residual, branch, weight, eps, out, update=True)
     _on_device(branch, residual, weight, out)
     width = residual.shape[-1]
     _f32_vector(weight, width, "the norm weight")
@@ -179,6 +194,56 @@ def add_rms_norm(branch, residual, weight, eps: float, out) -> None:
     _check(library.tau_add_rms_norm(_code(residual), _pointer(branch), _pointer(residual), _pointer(weight), _pointer(out),
                                     ctypes.c_int(residual.numel() // width), ctypes.c_int(width), ctypes.c_float(eps), _stream()),
            "add_rms_norm")
+
+
+def stream_add_norm(stream, branches, weight, eps: float, out, rows=None, update: bool = True) -> None:
+    """A residual stream kept in 32-bit: `sum = stream[r] + (a[r] + b[r])` in 32-bit for up to two branches of any dtype
+    (`branches`: None, a tensor or a tuple of one or two), `r = rows[i]` or `i`; with `update` (no `rows` then) the sum
+    replaces `stream[r]`; `out[i] = sum / sqrt(mean(sum^2) + eps) * weight`, rounded once to the output's dtype."""
+    if branches is None:
+        branches = ()
+    elif not isinstance(branches, (tuple, list)):
+        branches = (branches,)
+    branches = tuple(branch for branch in branches if branch is not None)
+    _require(len(branches) <= 2, "at most two branches join the stream at once")
+    _on_device(stream, weight, out, rows, *branches)
+    width = stream.shape[-1]
+    _f32_vector(weight, width, "the norm weight")
+    _require(stream.dtype == torch.float32 and stream.is_contiguous() and out.is_contiguous() and out.shape[-1] == width,
+             "the stream must be contiguous float32 and the output as wide")
+    for branch in branches:
+        _require(branch.shape == stream.shape and branch.is_contiguous(), "a branch must match the stream")
+    _require(not (update and rows is not None), "rows are gathered from a stream that is left as it is")
+    if rows is not None:
+        _int_vector(rows, "row numbers")
+    count = out.numel() // width
+    _require(count == (rows.shape[0] if rows is not None else stream.numel() // width), "output row count does not match")
+    first = branches[0] if branches else None
+    second = branches[1] if len(branches) > 1 else None
+    library = build.load_library("stream32.cu")
+    _check(library.tau_stream_add_norm(_code(out), _pointer(stream), _pointer(first), ctypes.c_int(_code(first) if first is not None else 0),
+                                       _pointer(second), ctypes.c_int(_code(second) if second is not None else 0), _pointer(rows), _pointer(weight),
+                                       _pointer(out), ctypes.c_int(count), ctypes.c_int(width), ctypes.c_float(eps), ctypes.c_int(1 if update else 0),
+                                       _stream()), "stream_add_norm")
+
+
+def gated_group_norm(values, weight, gate, out, groups: int, eps: float, normalize: bool) -> None:
+    """`values` [rows, width] in 32-bit; with `normalize` each of the `groups` equal parts of a row is divided by its root
+    mean square (eps inside the root); then times `weight` (float32 [width] or None), times `sigmoid(gate)` (the output's
+    dtype, [rows, width], rows any distance apart, or None); rounded once to the output's dtype."""
+    _on_device(values, weight, gate, out)
+    rows, width = values.shape
+    _require(values.dtype == torch.float32 and values.is_contiguous() and out.is_contiguous() and out.shape == values.shape,
+             "values must be contiguous float32 and the output of the same shape")
+    _require(groups > 0 and width % groups == 0, "the groups must divide the width")
+    _f32_vector(weight, width, "the weight")
+    if gate is not None:
+        _require(gate.dtype == out.dtype and gate.shape == values.shape and gate.stride(1) == 1, "the gate must have the output's dtype and shape")
+    library = build.load_library("stream32.cu")
+    _check(library.tau_gated_group_norm(_code(out), _pointer(values), _pointer(weight), _pointer(gate),
+                                        ctypes.c_longlong(0 if gate is None else gate.stride(0)), _pointer(out), ctypes.c_int(rows),
+                                        ctypes.c_int(groups), ctypes.c_int(width // groups), ctypes.c_float(eps), ctypes.c_int(1 if normalize else 0),
+                                        _stream()), "gated_group_norm")
 
 
 def silu_mul(stacked, out) -> None:
@@ -208,6 +273,22 @@ def gemm_simt(values, weight, bias, out) -> None:
                                  ctypes.c_int(rows), ctypes.c_int(features), ctypes.c_int(depth),
                                  ctypes.c_longlong(values.stride(0)), ctypes.c_longlong(weight.stride(0)),
                                  ctypes.c_longlong(out.stride(0)), _stream()), "gemm_simt")
+
+
+def gemm_simt_batched(values, weight, out) -> None:
+    """`out[:, b] = values[:, b] @ weight[b].T` for every `b` in one launch, on the 32-bit pipes: `values` [M, B, K],
+    `weight` [B, N, K], `out` [M, B, N]; the three may be views whose rows and batches lie any distance apart."""
+    _on_device(values, weight, out)
+    rows, batch, depth = values.shape
+    features = weight.shape[1]
+    _require(weight.shape == (batch, features, depth) and out.shape == (rows, batch, features), "shapes must be [M,B,K] x [B,N,K] -> [M,B,N]")
+    _require(values.dtype == weight.dtype and out.dtype in (values.dtype, torch.float32), "input and weight must have the same dtype")
+    library = build.load_library("gemm_simt.cu")
+    _check(library.tau_gemm_simt_batched(_code(values), _code(out), _pointer(values), _pointer(weight), _pointer(out), ctypes.c_int(rows),
+                                         ctypes.c_int(features), ctypes.c_int(depth), ctypes.c_longlong(values.stride(0)),
+                                         ctypes.c_longlong(weight.stride(1)), ctypes.c_longlong(out.stride(0)), ctypes.c_int(batch),
+                                         ctypes.c_longlong(values.stride(1)), ctypes.c_longlong(weight.stride(0)), ctypes.c_longlong(out.stride(1)),
+                                         _stream()), "gemm_simt_batched")
 
 
 SKINNY_MAX_ROWS = 32      # what the skinny kernel accepts
@@ -603,6 +684,165 @@ def attention(queries, keys, values, out, step, page_rows, n_heads: int, n_kv_he
         prefill = attention_prefill_tc if head_dim in (64, 128) and rows_fit else attention_prefill
         return prefill(queries, keys, values, out, step.cu_seqlens, step.seq_start, page_rows, n_heads, n_kv_heads, head_dim, scale, window)
     attention_generic(queries, keys, values, out, step.positions, step.token_seq, page_rows, n_heads, n_kv_heads, head_dim, scale, window)
+
+
+# ---------------------------------------------------------------------------- latent attention
+def latent_prepare(down, latent_weight, eps: float, q, queries, rows, inv_freq, rotary_dim: int, positions, token_seq, page_rows,
+                   n_heads: int, head_dim: int, rot_dim: int, rank: int, write_rows: bool = True) -> None:
+    """`down` [tokens, rank + rot_dim]: its first `rank` elements, RMS-normed with `latent_weight`, and its last `rot_dim`,
+    rotated, go to the token's row of the cache pages `rows` [pages, 64, rank + rot_dim].  `q` [tokens, n_heads *
+    (head_dim + rot_dim)]: each head's last `rot_dim` elements, rotated, go to `queries[token, head, rank:]`
+    (`queries` [tokens, n_heads, rank + rot_dim]; its first `rank` elements per head are another kernel's to fill).
+    The rotation turns the pair (2i, 2i + 1), i < rotary_dim / 2, by `position * inv_freq[i]`."""
+    _on_device(down, latent_weight, q, queries, rows, inv_freq, positions, token_seq, page_rows)
+    tokens, width = q.shape[0], rank + rot_dim
+    _require(q.shape[1] == n_heads * (head_dim + rot_dim) and queries.shape == (tokens, n_heads, width) and queries.is_contiguous()
+             and queries.dtype == q.dtype, "queries must be [tokens, n_heads, rank + rot_dim]")
+    _require(rotary_dim % 2 == 0 and 0 <= rotary_dim <= rot_dim, "rotary_dim must be even and at most rot_dim")
+    if rotary_dim:
+        _f32_vector(inv_freq, rotary_dim // 2, "the rotation's frequencies")
+    _int_vector(positions, "positions")
+    _int_vector(token_seq, "token_seq")
+    if write_rows:
+        _require(down.shape == (tokens, width) and down.dtype == q.dtype, "the down-projection must be [tokens, rank + rot_dim]")
+        _require(rows.shape[1:] == (PAGE_TOKENS, width) and rows.is_contiguous() and rows.dtype == q.dtype, "cache rows must be [pages, 64, rank + rot_dim]")
+        _f32_vector(latent_weight, rank, "the latent norm weight")
+        _require(page_rows.dtype == torch.int32 and page_rows.dim() == 2 and page_rows.is_contiguous(), "page rows must be int32 [sequences, stride]")
+    library = build.load_library("latent_attention.cu")
+    _check(library.tau_latent_prepare(
+        _code(q), _pointer(down), ctypes.c_longlong(down.stride(0) if write_rows else 0), _pointer(latent_weight), ctypes.c_float(eps), _pointer(q),
+        ctypes.c_longlong(q.stride(0)), _pointer(queries), _pointer(rows), _pointer(inv_freq), ctypes.c_int(rotary_dim), _pointer(positions),
+        _pointer(token_seq), _pointer(page_rows), ctypes.c_int(page_rows.shape[1]), ctypes.c_int(PAGE_TOKENS), ctypes.c_int(tokens),
+        ctypes.c_int(n_heads), ctypes.c_int(head_dim), ctypes.c_int(rot_dim), ctypes.c_int(rank), ctypes.c_int(1 if write_rows else 0), _stream()),
+        "latent_prepare")
+
+
+LATENT_MAX_RANK = 512   # what the latent attention kernel keeps per lane
+
+
+def latent_attention(queries, rows, out, sinks, positions, token_seq, page_rows, n_heads: int, rank: int, rot_dim: int, scale: float,
+                     window: int = 0) -> None:
+    """Causal softmax attention of `queries` [tokens, n_heads, rank + rot_dim] over the cached rows [pages, 64, rank + rot_dim]
+    of each token's sequence; a score is the dot product of a query with a row times `scale`; `out` [tokens, n_heads, rank]
+    receives the weighted sums of the rows' first `rank` elements.  `sinks` (float32 [n_heads] or None): `exp(sink)` joins
+    the softmax denominator.  Scores, weights and sums are 32-bit."""
+    _on_device(queries, rows, out, sinks, positions, token_seq, page_rows)
+    tokens, width = queries.shape[0], rank + rot_dim
+    _require(queries.shape == (tokens, n_heads, width) and queries.is_contiguous() and out.shape == (tokens, n_heads, rank) and out.is_contiguous()
+             and out.dtype == queries.dtype == rows.dtype, "queries must be [tokens, n_heads, rank + rot_dim] and the output [tokens, n_heads, rank]")
+    _require(rows.shape[1:] == (PAGE_TOKENS, width) and rows.is_contiguous(), "cache rows must be [pages, 64, rank + rot_dim]")
+    _require(rank <= LATENT_MAX_RANK, f"the latent may have at most {LATENT_MAX_RANK} elements")
+    _f32_vector(sinks, n_heads, "the sinks")
+    _int_vector(positions, "positions")
+    _int_vector(token_seq, "token_seq")
+    _require(page_rows.dtype == torch.int32 and page_rows.dim() == 2 and page_rows.is_contiguous(), "page rows must be int32 [sequences, stride]")
+    library = build.load_library("latent_attention.cu")
+    _check(library.tau_latent_attention(
+        _code(queries), _pointer(queries), _pointer(rows), _pointer(out), _pointer(sinks), _pointer(positions), _pointer(token_seq),
+        _pointer(page_rows), ctypes.c_int(page_rows.shape[1]), ctypes.c_int(PAGE_TOKENS), ctypes.c_int(tokens), ctypes.c_int(n_heads),
+        ctypes.c_int(rank), ctypes.c_int(rot_dim), ctypes.c_float(scale), ctypes.c_int(window), _stream()), "latent_attention")
+
+
+# ---------------------------------------------------------------------------- linear recurrences
+RECURRENCE_MAX_KEY_DIM = 512
+
+
+def linear_recurrence(q, k, v, gates, decays, state, cu_seqlens, seq_slot, out, n_heads: int, key_dim: int, value_dim: int,
+                      exponential: bool, gate_cap: float = 0.0, query_scale: float = 1.0, silu: bool = False) -> None:
+    """Advances the matrix state of every (sequence, head) over the sequence's new tokens and writes each token's read-out.
+
+    `q`, `k` [tokens, n_heads * key_dim] and `v` [tokens, n_heads * value_dim] may be column ranges of one wider tensor (same
+    row stride).  `state` [slots, floats per slot] is 32-bit and updated in place: per head `value_dim` columns of `key_dim`
+    numbers, and with `exponential` one more column (the normaliser) and the running maximum.  `gates` [tokens, 2 * n_heads]
+    float32 are the pre-activations of the input gates, then of the forget gates; `decays` [n_heads] float32 otherwise.
+    `out` [tokens, n_heads * value_dim] float32."""
+    _on_device(q, k, v, gates, decays, state, cu_seqlens, seq_slot, out)
+    tokens = q.shape[0]
+    _require(q.shape == (tokens, n_heads * key_dim) == k.shape and v.shape == (tokens, n_heads * value_dim), "q, k must be [tokens, heads * key_dim], v [tokens, heads * value_dim]")
+    _require(q.dtype == k.dtype == v.dtype and q.stride(0) == k.stride(0) == v.stride(0), "q, k and v must share dtype and row stride")
+    _require(1 <= key_dim <= RECURRENCE_MAX_KEY_DIM, f"key_dim must lie between 1 and {RECURRENCE_MAX_KEY_DIM}")
+    per_head = (value_dim + 1) * key_dim + 1 if exponential else value_dim * key_dim
+    _require(state.dtype == torch.float32 and state.dim() == 2 and state.is_contiguous() and state.shape[1] == n_heads * per_head,
+             f"the state must be float32 [slots, {n_heads * per_head}]")
+    _require(out.shape == (tokens, n_heads * value_dim) and out.dtype == torch.float32 and out.is_contiguous(), "the output must be float32 [tokens, heads * value_dim]")
+    if exponential:
+        _require(gates is not None and gates.shape == (tokens, 2 * n_heads) and gates.dtype == torch.float32 and gates.is_contiguous(),
+                 "gates must be float32 [tokens, 2 * heads]")
+        _require(value_dim + 1 <= 128, "with exponential gating a head may have at most 127 value elements")
+    else:
+        _f32_vector(decays, n_heads, "the decays")
+        _require(decays is not None, "decays are needed")
+    _int_vector(cu_seqlens, "cu_seqlens")
+    _int_vector(seq_slot, "seq_slot")
+    n_seqs = seq_slot.numel()
+    _require(cu_seqlens.numel() == n_seqs + 1, "one run per sequence")
+    library = build.load_library("recurrence.cu", (f"TAU_KEY_DIM={key_dim}",))
+    _check(library.tau_linear_recurrence(
+        _code(q), _pointer(q), _pointer(k), _pointer(v), ctypes.c_longlong(q.stride(0)), _pointer(gates), _pointer(decays), _pointer(state),
+        ctypes.c_longlong(state.stride(0)), _pointer(cu_seqlens), _pointer(seq_slot), _pointer(out), ctypes.c_int(n_seqs), ctypes.c_int(n_heads),
+        ctypes.c_int(value_dim), ctypes.c_int(1 if exponential else 0), ctypes.c_float(gate_cap), ctypes.c_float(query_scale),
+        ctypes.c_int(1 if silu else 0), _stream()), "linear_recurrence")
+
+
+# ---------------------------------------------------------------------------- routed experts
+def moe_route(hidden, router, correction, shared_gate_weight, chosen, weights, shared_gate, top: int, softmax: bool = False,
+              renormalize: bool = False) -> None:
+    """Scores the experts of every token in 32-bit and chooses `top` of them: `router` float32 [experts, width];
+    scores = sigmoid (or softmax) of `router @ hidden`; chosen by score + `correction` (float32 [experts] or None), the
+    lowest index among equals; `weights` are the chosen scores themselves (divided by their sum with `renormalize`).
+    `shared_gate[token] = sigmoid(shared_gate_weight . hidden[token])` where that weight (float32 [width]) is given."""
+    _on_device(hidden, router, correction, shared_gate_weight, chosen, weights, shared_gate)
+    tokens, width = hidden.shape
+    experts = router.shape[0]
+    _require(hidden.is_contiguous() and router.dtype == torch.float32 and router.shape == (experts, width) and router.is_contiguous(),
+             "the router must be float32 [experts, width]")
+    _f32_vector(correction, experts, "the correction")
+    _f32_vector(shared_gate_weight, width, "the shared gate's weight")
+    _require(chosen.dtype == torch.int32 and chosen.shape == (tokens, top) and chosen.is_contiguous() and weights.dtype == torch.float32
+             and weights.shape == (tokens, top) and weights.is_contiguous(), "chosen must be int32 and weights float32, both [tokens, top]")
+    if shared_gate_weight is not None:
+        _require(shared_gate is not None and shared_gate.dtype == torch.float32 and shared_gate.numel() == tokens, "one shared gate per token")
+    library = build.load_library("moe.cu")
+    _check(library.tau_moe_route(_code(hidden), _pointer(hidden), _pointer(router), _pointer(correction), _pointer(shared_gate_weight),
+                                 _pointer(chosen), _pointer(weights), _pointer(shared_gate), ctypes.c_int(tokens), ctypes.c_int(width),
+                                 ctypes.c_int(experts), ctypes.c_int(top), ctypes.c_int(1 if softmax else 0), ctypes.c_int(1 if renormalize else 0),
+                                 _stream()), "moe_route")
+
+
+def moe_gate_up(hidden, gate_up, chosen, inner) -> None:
+    """`inner[token, place] = silu(gate_e @ h) * (up_e @ h)` with `e = chosen[token, place]`; `gate_up` [experts, 2 * I, width]
+    holds each expert's gate rows, then its up rows; `inner` [tokens, top, I]."""
+    _on_device(hidden, gate_up, chosen, inner)
+    tokens, width = hidden.shape
+    top, size = inner.shape[1], inner.shape[2]
+    _require(hidden.is_contiguous() and gate_up.is_contiguous() and inner.is_contiguous() and hidden.dtype == gate_up.dtype == inner.dtype,
+             "tensors must be contiguous and of one dtype")
+    _require(gate_up.shape[1:] == (2 * size, width) and inner.shape[0] == tokens and chosen.shape == (tokens, top) and chosen.dtype == torch.int32
+             and chosen.is_contiguous(), "shapes must be [T,W], [E,2I,W], [T,top] -> [T,top,I]")
+    library = build.load_library("moe.cu")
+    _check(library.tau_moe_gate_up(_code(hidden), _pointer(hidden), _pointer(gate_up), _pointer(chosen), _pointer(inner), ctypes.c_int(tokens),
+                                   ctypes.c_int(width), ctypes.c_int(size), ctypes.c_int(top), _stream()), "moe_gate_up")
+
+
+def moe_down(inner, down, chosen, weights, shared_out, shared_gate, out) -> None:
+    """`out[token] = sum_place weights[token, place] * (down_e @ inner[token, place]) + shared_gate[token] * shared_out[token]`,
+    float32 [tokens, width]; `down` [experts, width, I]; `shared_out` (the activations' dtype) and `shared_gate` (float32
+    [tokens]; None: 1) are optional."""
+    _on_device(inner, down, chosen, weights, shared_out, shared_gate, out)
+    tokens, top, size = inner.shape
+    width = down.shape[1]
+    _require(inner.is_contiguous() and down.is_contiguous() and inner.dtype == down.dtype and down.shape[2] == size, "down must be [experts, width, I]")
+    _require(out.shape == (tokens, width) and out.dtype == torch.float32 and out.is_contiguous(), "the output must be float32 [tokens, width]")
+    _require(chosen.shape == (tokens, top) and chosen.dtype == torch.int32 and chosen.is_contiguous() and weights.shape == (tokens, top)
+             and weights.dtype == torch.float32 and weights.is_contiguous(), "chosen and weights must be [tokens, top]")
+    if shared_out is not None:
+        _require(shared_out.shape == (tokens, width) and shared_out.dtype == inner.dtype and shared_out.is_contiguous(), "the shared output must be [tokens, width]")
+    if shared_gate is not None:
+        _require(shared_gate.dtype == torch.float32 and shared_gate.numel() == tokens and shared_gate.is_contiguous(), "one shared gate per token")
+    library = build.load_library("moe.cu")
+    _check(library.tau_moe_down(_code(inner), _pointer(inner), _pointer(down), _pointer(chosen), _pointer(weights), _pointer(shared_out),
+                                _pointer(shared_gate), _pointer(out), ctypes.c_int(tokens), ctypes.c_int(width), ctypes.c_int(size), ctypes.c_int(top),
+                                _stream()), "moe_down")
 
 
 # ---------------------------------------------------------------------------- random weights

@@ -13,6 +13,10 @@ def all_libraries() -> List[Tuple[str, Sequence[str]]]:
         ("attention_generic.cu", ()),
         ("sampling.cu", ()),
         ("random_init.cu", ()),
+        ("stream32.cu", ()),
+        ("latent_attention.cu", ()),
+        ("moe.cu", ()),
+        *[("recurrence.cu", (f"TAU_KEY_DIM={key_dim}",)) for key_dim in (16, 32, 64, 128)],
         # Specialised libraries: the head sizes of the benchmark shape and of the tests' tiny models.
         *[("attention_decode.cu", (f"TAU_HEAD_DIM={head_dim}", f"TAU_DTYPE={dtype}"))
           for head_dim in (128, 64, 16, 32, 48) for dtype in (0, 1)],

@@ -1,0 +1,195 @@
+// Routed experts, token by token: a router that scores the experts in 32-bit and picks `top` of them, the chosen
+// experts' gated products, and the weighted sum of their outputs (plus a shared expert's, scaled by its own gate).
+//
+//   route:    z = W_router h (32-bit weights and sums); s = sigmoid(z) or softmax(z); the `top` largest of
+//             s + correction are chosen (the lowest index among equals), their weights are s itself, divided by
+//             their sum if `renormalize`; shared_gate = sigmoid(w_sg . h).
+//   gate_up:  inner[token, place] = silu(W_gate[e] h) * (W_up[e] h) for the expert e of each (token, place).
+//   down:     out[token] = sum over places of weight * (W_down[e] inner[token, place]) + shared_gate * shared[token], 32-bit.
+//
+// These are weight-streaming kernels: a warp per output feature, the activation row in shared memory as floats.
+#include "common.cuh"
+
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kWarps = kThreads / 32;
+
+// Dot product of a weight row with a float vector in shared memory, over the warp.
+template <typename T>
+__device__ __forceinline__ float warp_dot(const T* __restrict__ weights, const float* __restrict__ vector, int length, int lane) {
+    float sum = 0.0f;
+    for (int column = lane; column < length; column += 32) sum = fmaf(to_float(weights[column]), vector[column], sum);
+    return warp_sum(sum);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+moe_route_kernel(const T* __restrict__ hidden, const float* __restrict__ router, const float* __restrict__ correction,
+                 const float* __restrict__ shared_gate_weight, int* __restrict__ chosen, float* __restrict__ weights, float* __restrict__ shared_gate,
+                 int width, int experts, int top, int softmax, int renormalize) {
+    grid_dependents_launch();
+    grid_dependency_wait();
+    extern __shared__ float shared[];
+    float* row = shared;               // [width]
+    float* scores = shared + width;    // [experts]
+    float* choice = scores + experts;  // [experts]
+    const int token = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int column = threadIdx.x; column < width; column += blockDim.x) row[column] = to_float(hidden[static_cast<size_t>(token) * width + column]);
+    __syncthreads();
+    for (int expert = warp; expert < experts; expert += kWarps) {
+        const float z = warp_dot(router + static_cast<size_t>(expert) * width, row, width, lane);
+        if (lane == 0) scores[expert] = z;
+    }
+    if (shared_gate_weight && warp == kWarps - 1) {
+        const float z = warp_dot(shared_gate_weight, row, width, lane);
+        if (lane == 0) shared_gate[token] = 1.0f / (1.0f + expf(-z));
+    }
+    __syncthreads();
+    if (warp != 0) return;
+    if (softmax) {
+        float top_z = -INFINITY;
+        for (int expert = lane; expert < experts; expert += 32) top_z = fmaxf(top_z, scores[expert]);
+        top_z = warp_max(top_z);
+        float total = 0.0f;
+        for (int expert = lane; expert < experts; expert += 32) total += expf(scores[expert] - top_z);
+        total = warp_sum(total);
+        for (int expert = lane; expert < experts; expert += 32) scores[expert] = expf(scores[expert] - top_z) / total;
+    } else {
+        for (int expert = lane; expert < experts; expert += 32) scores[expert] = 1.0f / (1.0f + expf(-scores[expert]));
+    }
+    for (int expert = lane; expert < experts; expert += 32) choice[expert] = scores[expert] + (correction ? correction[expert] : 0.0f);
+    __syncwarp();
+    float total = 0.0f;
+    for (int place = 0; place < top; ++place) {
+        float best = -INFINITY;
+        int best_expert = 0x7fffffff;
+        for (int expert = lane; expert < experts; expert += 32) {
+            const float value = choice[expert];
+            if (value > best) { best = value; best_expert = expert; }   // ascending scan: the lowest index among equals stays
+        }
+#pragma unroll
+        for (int offset = 16; offset > 0; offset >>= 1) {
+            const float other = __shfl_xor_sync(0xffffffffu, best, offset);
+            const int other_expert = __shfl_xor_sync(0xffffffffu, best_expert, offset);
+            if (other > best || (other == best && other_expert < best_expert)) { best = other; best_expert = other_expert; }
+        }
+        if (best_expert >= experts) best_expert = place;     // only rows of NaN come here
+        if (lane == 0) {
+            chosen[static_cast<size_t>(token) * top + place] = best_expert;
+            weights[static_cast<size_t>(token) * top + place] = scores[best_expert];
+            choice[best_expert] = -INFINITY;
+        }
+        total += scores[best_expert];
+        __syncwarp();
+    }
+    if (renormalize && lane == 0)
+        for (int place = 0; place < top; ++place) weights[static_cast<size_t>(token) * top + place] /= total;
+}
+
+// grid (token-place pairs, feature tiles).  gate_up: [experts, 2 * inner, width], gate rows first.
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+moe_gate_up_kernel(const T* __restrict__ hidden, const T* __restrict__ gate_up, const int* __restrict__ chosen, T* __restrict__ inner_out,
+                   int width, int inner, int top, int features_per_block) {
+    grid_dependents_launch();
+    grid_dependency_wait();
+    extern __shared__ float row[];
+    const int pair = blockIdx.x, token = pair / top, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int column = threadIdx.x; column < width; column += blockDim.x) row[column] = to_float(hidden[static_cast<size_t>(token) * width + column]);
+    __syncthreads();
+    const T* weights = gate_up + static_cast<size_t>(chosen[pair]) * 2 * inner * width;
+    const int begin = blockIdx.y * features_per_block, end = min(inner, begin + features_per_block);
+    for (int feature = begin + warp; feature < end; feature += kWarps) {
+        const float gate = warp_dot(weights + static_cast<size_t>(feature) * width, row, width, lane);
+        const float up = warp_dot(weights + static_cast<size_t>(inner + feature) * width, row, width, lane);
+        if (lane == 0) inner_out[static_cast<size_t>(pair) * inner + feature] = from_float<T>(gate / (1.0f + expf(-gate)) * up);
+    }
+}
+
+// grid (tokens, feature tiles).  down: [experts, width, inner].
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+moe_down_kernel(const T* __restrict__ inner_in, const T* __restrict__ down, const int* __restrict__ chosen, const float* __restrict__ weights,
+                const T* __restrict__ shared_out, const float* __restrict__ shared_gate, float* __restrict__ out, int width, int inner, int top,
+                int features_per_block) {
+    grid_dependents_launch();
+    grid_dependency_wait();
+    extern __shared__ float rows[];     // [top][inner]
+    const int token = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int item = threadIdx.x; item < top * inner; item += blockDim.x) rows[item] = to_float(inner_in[static_cast<size_t>(token) * top * inner + item]);
+    __syncthreads();
+    const int begin = blockIdx.y * features_per_block, end = min(width, begin + features_per_block);
+    for (int feature = begin + warp; feature < end; feature += kWarps) {
+        float sum = 0.0f;
+        for (int place = 0; place < top; ++place) {
+            const T* weight_row = down + (static_cast<size_t>(chosen[static_cast<size_t>(token) * top + place]) * width + feature) * inner;
+            sum = fmaf(weights[static_cast<size_t>(token) * top + place], warp_dot(weight_row, rows + place * inner, inner, lane), sum);
+        }
+        if (lane == 0) {
+            if (shared_out) sum += (shared_gate ? shared_gate[token] : 1.0f) * to_float(shared_out[static_cast<size_t>(token) * width + feature]);
+            out[static_cast<size_t>(token) * width + feature] = sum;
+        }
+    }
+}
+
+template <typename T>
+int launch_all(int what, const void* a, const void* b, const void* c, const void* d, const void* e, const void* f, void* o1, void* o2, void* o3,
+               int tokens, int width, int inner, int experts, int top, int flag_a, int flag_b, cudaStream_t s) {
+    if (what == 0) {
+        const size_t bytes = (static_cast<size_t>(width) + 2 * experts) * sizeof(float);
+        if (bytes > 48 * 1024 && cudaFuncSetAttribute(moe_route_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes)) != cudaSuccess)
+            return cudaErrorInvalidValue;
+        tau_launch(moe_route_kernel<T>, dim3(tokens), dim3(kThreads), bytes, s, static_cast<const T*>(a), static_cast<const float*>(b), static_cast<const float*>(c),
+                   static_cast<const float*>(d), static_cast<int*>(o1), static_cast<float*>(o2), static_cast<float*>(o3), width, experts, top, flag_a, flag_b);
+    } else if (what == 1) {
+        const int per_block = 64;
+        const size_t bytes = static_cast<size_t>(width) * sizeof(float);
+        if (bytes > 48 * 1024 && cudaFuncSetAttribute(moe_gate_up_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes)) != cudaSuccess)
+            return cudaErrorInvalidValue;
+        tau_launch(moe_gate_up_kernel<T>, dim3(tokens * top, (inner + per_block - 1) / per_block), dim3(kThreads), bytes, s, static_cast<const T*>(a),
+                   static_cast<const T*>(b), static_cast<const int*>(c), static_cast<T*>(o1), width, inner, top, per_block);
+    } else {
+        const int per_block = 64;
+        const size_t bytes = static_cast<size_t>(top) * inner * sizeof(float);
+        if (bytes > 48 * 1024 && cudaFuncSetAttribute(moe_down_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes)) != cudaSuccess)
+            return cudaErrorInvalidValue;
+        tau_launch(moe_down_kernel<T>, dim3(tokens, (width + per_block - 1) / per_block), dim3(kThreads), bytes, s, static_cast<const T*>(a), static_cast<const T*>(b),
+                   static_cast<const int*>(c), static_cast<const float*>(d), static_cast<const T*>(e), static_cast<const float*>(f), static_cast<float*>(o1),
+                   width, inner, top, per_block);
+    }
+    return tau_launch_status();
+}
+
+}  // namespace
+
+TAU_EXPORT int tau_moe_route(int dtype, const void* hidden, const float* router, const float* correction, const float* shared_gate_weight, int* chosen,
+                             float* weights, float* shared_gate, int tokens, int width, int experts, int top, int softmax, int renormalize, void* stream) {
+    if (tokens <= 0) return 0;
+    if (!hidden || !router || !chosen || !weights || width <= 0 || experts <= 0 || top <= 0 || top > experts || (shared_gate_weight && !shared_gate))
+        return cudaErrorInvalidValue;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (dtype == TAU_F32) return launch_all<float>(0, hidden, router, correction, shared_gate_weight, nullptr, nullptr, chosen, weights, shared_gate, tokens, width, 0, experts, top, softmax, renormalize, s);
+    if (dtype == TAU_BF16) return launch_all<bf16>(0, hidden, router, correction, shared_gate_weight, nullptr, nullptr, chosen, weights, shared_gate, tokens, width, 0, experts, top, softmax, renormalize, s);
+    return cudaErrorInvalidValue;
+}
+
+TAU_EXPORT int tau_moe_gate_up(int dtype, const void* hidden, const void* gate_up, const int* chosen, void* inner_out, int tokens, int width, int inner,
+                               int top, void* stream) {
+    if (tokens <= 0) return 0;
+    if (!hidden || !gate_up || !chosen || !inner_out || width <= 0 || inner <= 0 || top <= 0 || static_cast<long long>(tokens) * top > 0x7fffffff) return cudaErrorInvalidValue;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (dtype == TAU_F32) return launch_all<float>(1, hidden, gate_up, chosen, nullptr, nullptr, nullptr, inner_out, nullptr, nullptr, tokens, width, inner, 0, top, 0, 0, s);
+    if (dtype == TAU_BF16) return launch_all<bf16>(1, hidden, gate_up, chosen, nullptr, nullptr, nullptr, inner_out, nullptr, nullptr, tokens, width, inner, 0, top, 0, 0, s);
+    return cudaErrorInvalidValue;
+}
+
+TAU_EXPORT int tau_moe_down(int dtype, const void* inner_in, const void* down, const int* chosen, const float* weights, const void* shared_out,
+                            const float* shared_gate, float* out, int tokens, int width, int inner, int top, void* stream) {
+    if (tokens <= 0) return 0;
+    if (!inner_in || !down || !chosen || !weights || !out || width <= 0 || inner <= 0 || top <= 0) return cudaErrorInvalidValue;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (dtype == TAU_F32) return launch_all<float>(2, inner_in, down, chosen, weights, shared_out, shared_gate, out, nullptr, nullptr, tokens, width, inner, 0, top, 0, 0, s);
+    if (dtype == TAU_BF16) return launch_all<bf16>(2, inner_in, down, chosen, weights, shared_out, shared_gate, out, nullptr, nullptr, tokens, width, inner, 0, top, 0, 0, s);
+    return cudaErrorInvalidValue;
+}

@@ -1,0 +1,130 @@
+// Linear recurrences with a matrix state per head, for runs of new tokens and for single tokens alike:
+//
+//     S_t = a_t S_(t-1) + b_t k_t v_t^T          o_t = S_t^T q_t            (S is key_dim x value_dim)
+//
+// Two gatings.  Decay: a_t is a constant of the head, b_t = 1 (linear attention with a decay per head).
+// Exponential: a log input gate i_t and a log forget gate f_t per head and token, both from soft-capped
+// pre-activations (i = cap tanh(x / cap), f = logsigmoid(cap tanh(y / cap))), a running maximum
+// m_t = max(f_t + m_(t-1), i_t) that starts at 0, a_t = exp(f_t + m_(t-1) - m_t), b_t = exp(i_t - m_t), a normaliser
+// n_t = a_t n_(t-1) + b_t k_t, and o_t = S_t^T q_t / (max(|n_t . q_t|, exp(-m_t)) + 1e-6).
+//
+// The state is 32-bit and lives in the cache, one record per (slot, head): value_dim (+1) columns of key_dim
+// numbers each, the extra column being n (which obeys the recurrence of a value that is always 1), then m.
+// One block owns a (sequence, head, tile of columns) and walks the sequence's new tokens in order; a thread keeps
+// its share of one column in registers, so a token costs one pass over key_dim per thread and two barriers.
+// Everything is computed in 32-bit; q, k, v arrive in the activations' dtype.  TAU_KEY_DIM fixes key_dim.
+#include "common.cuh"
+
+#ifndef TAU_KEY_DIM
+#error "compile with -DTAU_KEY_DIM=<key elements per head>"
+#endif
+
+namespace {
+
+constexpr int kDim = TAU_KEY_DIM;
+constexpr int kSplit = kDim <= 64 ? 1 : kDim <= 128 ? 2 : kDim <= 256 ? 4 : 8;   // threads that share a column
+constexpr int kRows = (kDim + kSplit - 1) / kSplit;                               // key rows per thread
+constexpr int kColumns = 128;                                                     // columns of a block (n included)
+
+__device__ __forceinline__ float activate(float value, int activation) { return activation ? value / (1.0f + expf(-value)) : value; }
+
+template <typename T>
+__global__ void __launch_bounds__(kColumns * kSplit)
+linear_recurrence_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, long long stride,
+                         const float* __restrict__ gates, const float* __restrict__ decays, float* __restrict__ state, long long slot_stride,
+                         const int* __restrict__ cu_seqlens, const int* __restrict__ seq_slot, float* __restrict__ out,
+                         int heads, int value_dim, int exponential, float gate_cap, float query_scale, int activation) {
+    grid_dependents_launch();
+    grid_dependency_wait();
+    __shared__ float qs[kDim], ks[kDim], partial[kSplit][kColumns], scalars[4];
+    const int head = blockIdx.x, sequence = blockIdx.y;
+    const int columns = value_dim + (exponential ? 1 : 0);           // n rides as one more column
+    const int column = blockIdx.z * kColumns + threadIdx.x % kColumns;
+    const int part = threadIdx.x / kColumns, row0 = part * kRows;
+    const bool live = column < columns;
+    const bool is_n = exponential && column == value_dim;
+    float* record = state + static_cast<size_t>(seq_slot[sequence]) * slot_stride + static_cast<size_t>(head) * (static_cast<size_t>(columns) * kDim + (exponential ? 1 : 0));
+    float S[kRows];
+#pragma unroll
+    for (int r = 0; r < kRows; ++r) S[r] = (live && row0 + r < kDim) ? record[static_cast<size_t>(column) * kDim + row0 + r] : 0.0f;
+    float m = exponential ? record[static_cast<size_t>(columns) * kDim] : 0.0f;
+    const float decay = exponential ? 1.0f : decays[head];
+    const int begin = cu_seqlens[sequence], end = cu_seqlens[sequence + 1];
+    for (int token = begin; token < end; ++token) {
+        const size_t row = static_cast<size_t>(token) * stride;
+        for (int d = threadIdx.x; d < kDim; d += blockDim.x) {
+            qs[d] = activate(to_float(q[row + head * kDim + d]), activation) * query_scale;
+            ks[d] = activate(to_float(k[row + head * kDim + d]), activation);
+        }
+        float keep = decay, take = 1.0f;
+        if (exponential) {
+            const float log_in = gate_cap * tanhf(gates[static_cast<size_t>(token) * 2 * heads + head] / gate_cap);
+            const float capped = gate_cap * tanhf(gates[static_cast<size_t>(token) * 2 * heads + heads + head] / gate_cap);
+            const float log_forget = fminf(capped, 0.0f) - log1pf(expf(-fabsf(capped)));     // logsigmoid
+            const float m_new = fmaxf(log_forget + m, log_in);
+            keep = expf(log_forget + m - m_new);
+            take = expf(log_in - m_new);
+            m = m_new;
+        }
+        __syncthreads();
+        const float value = is_n ? 1.0f : live ? activate(to_float(v[row + head * value_dim + column]), activation) : 0.0f;
+        const float scaled = take * value;
+        float sum = 0.0f;
+#pragma unroll
+        for (int r = 0; r < kRows; ++r) {
+            if (row0 + r < kDim) {
+                S[r] = fmaf(keep, S[r], ks[row0 + r] * scaled);
+                sum = fmaf(S[r], qs[row0 + r], sum);
+            }
+        }
+        if (kSplit > 1) {
+            partial[part][threadIdx.x % kColumns] = sum;
+            __syncthreads();
+            sum = 0.0f;
+#pragma unroll
+            for (int p = 0; p < kSplit; ++p) sum += partial[p][threadIdx.x % kColumns];
+        }
+        if (exponential) {
+            if (is_n && part == 0) scalars[0] = fmaxf(fabsf(sum), expf(-m)) + 1e-6f;
+            __syncthreads();
+            sum /= scalars[0];
+        }
+        if (live && !is_n && part == 0) out[static_cast<size_t>(token) * heads * value_dim + head * value_dim + column] = sum;
+        __syncthreads();    // qs, ks, partial and scalars are written again for the next token
+    }
+    if (live) {
+#pragma unroll
+        for (int r = 0; r < kRows; ++r)
+            if (row0 + r < kDim) record[static_cast<size_t>(column) * kDim + row0 + r] = S[r];
+    }
+    if (exponential && blockIdx.z == 0 && threadIdx.x == 0) record[static_cast<size_t>(columns) * kDim] = m;
+}
+
+}  // namespace
+
+TAU_EXPORT int tau_recurrence_key_dim() { return kDim; }
+
+// q, k, v: rows `stride` elements apart, heads side by side.  gates [tokens, 2 heads] (exponential) or decays [heads].
+// state: records `slot_stride` floats apart per slot.  out [tokens, heads * value_dim], 32-bit.
+TAU_EXPORT int tau_linear_recurrence(int dtype, const void* q, const void* k, const void* v, long long stride, const float* gates,
+                                     const float* decays, float* state, long long slot_stride, const int* cu_seqlens, const int* seq_slot,
+                                     float* out, int n_seqs, int heads, int value_dim, int exponential, float gate_cap, float query_scale,
+                                     int activation, void* stream) {
+    if (n_seqs <= 0) return 0;
+    if (!q || !k || !v || !state || !cu_seqlens || !seq_slot || !out || heads <= 0 || value_dim <= 0 || (exponential ? !gates : !decays))
+        return cudaErrorInvalidValue;
+    // With the exponential gating every block needs the n column; the tiles after the first would not have it.
+    const int columns = value_dim + (exponential ? 1 : 0);
+    if (exponential && columns > kColumns) return cudaErrorInvalidValue;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    dim3 grid(heads, n_seqs, (columns + kColumns - 1) / kColumns), block(kColumns * kSplit);
+    if (dtype == TAU_F32)
+        tau_launch(linear_recurrence_kernel<float>, grid, block, 0, s, static_cast<const float*>(q), static_cast<const float*>(k), static_cast<const float*>(v),
+                   stride, gates, decays, state, slot_stride, cu_seqlens, seq_slot, out, heads, value_dim, exponential, gate_cap, query_scale, activation);
+    else if (dtype == TAU_BF16)
+        tau_launch(linear_recurrence_kernel<bf16>, grid, block, 0, s, static_cast<const bf16*>(q), static_cast<const bf16*>(k), static_cast<const bf16*>(v),
+                   stride, gates, decays, state, slot_stride, cu_seqlens, seq_slot, out, heads, value_dim, exponential, gate_cap, query_scale, activation);
+    else
+        return cudaErrorInvalidValue;
+    return tau_launch_status();
+}

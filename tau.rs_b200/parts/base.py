@@ -20,8 +20,10 @@ class CacheNeed:
     """What a mixer wants the cache to keep for it, per cache layer.
 
     `kind == "kv"`: keys and values of `n_kv_heads` heads of `head_dim` elements for
-    every position (or for the last `window` positions).  `kind == "state"`: one
-    tensor of `state_shape` and `state_dtype` for each sequence, zero when the sequence
+    every position (or for the last `window` positions).  `kind == "rows"`: one row of
+    `row_width` elements for every position (or for the last `window`), paged like keys
+    and values (a latent that keys and values are expanded from, say).  `kind == "state"`:
+    one tensor of `state_shape` and `state_dtype` for each sequence, zero when the sequence
     starts, whatever its length.
     """
 
@@ -31,6 +33,7 @@ class CacheNeed:
     window: Optional[int] = None
     state_shape: Tuple[int, ...] = ()
     state_dtype: torch.dtype = torch.float32
+    row_width: int = 0
 
 
 class Part:

@@ -66,3 +66,42 @@ class PreNormBlock(Block):
         mixed = self.mixer.forward(normalized, step, cache, writes_cache)
         normalized = self.feed_forward_norm.add_forward(mixed, residual)
         return residual, self.feed_forward.forward(normalized, step)
+
+
+@register_block("parallel")
+class ParallelBlock(Block):
+    """One norm, two readers: `h = norm(x)`, `x <- x + (mixer(h) + feed_forward(h))`; the feed-forward may be absent.
+
+    The residual stream `x` is 32-bit whatever the activations' dtype.  The block hands on `(x, (mixer's output,
+    feed-forward's output))`; the next block's norm (or the model's last one) adds the two in 32-bit, adds that to the
+    stream and normalises, in one kernel.  Weight names: `<prefix>.norm1`, `<prefix>.mix.*`, `<prefix>.mlp.*`.
+    """
+
+    mixer_name = "mix"
+    feed_forward_name = "mlp"
+    norm_name = "norm1"
+
+    def __init__(self, spec, dtype, device):
+        self.spec = spec
+        prefix = spec.prefix
+        self.norm = build("norm", spec.mixer_norm, name=f"{prefix}.{self.norm_name}", dtype=dtype, device=device)
+        self.mixer = build("mixer", spec.mixer, prefix=f"{prefix}.{self.mixer_name}", dtype=dtype, device=device)
+        self.feed_forward = None
+        if spec.feed_forward is not None:
+            self.feed_forward = build("feed_forward", spec.feed_forward, prefix=f"{prefix}.{self.feed_forward_name}", dtype=dtype, device=device)
+        self._children = tuple(part for part in (self.norm, self.mixer, self.feed_forward) if part is not None)
+        self.capturable = all(getattr(part, "capturable", True) for part in self._children)
+
+    cache_need = PreNormBlock.cache_need
+    decode_blocks = PreNormBlock.decode_blocks
+    tensor_specs = PreNormBlock.tensor_specs
+    assign = PreNormBlock.assign
+    finalize_weights = PreNormBlock.finalize_weights
+    bytes_read_per_step = PreNormBlock.bytes_read_per_step
+
+    def forward(self, residual, branch, step, cache, writes_cache: bool):
+        normalized = self.norm.forward(residual) if branch is None else self.norm.add_forward(branch, residual)
+        mixed = self.mixer.forward(normalized, step, cache, writes_cache)
+        if self.feed_forward is None:
+            return residual, mixed
+        return residual, (mixed, self.feed_forward.forward(normalized, step))

@@ -23,10 +23,12 @@ class StackedLinear(Part):
     `<prefix>.bias` if `bias`) are stacked along the output axis in that order.
     """
 
-    def __init__(self, pieces: Sequence[Tuple[str, int]], in_features: int, bias: bool, dtype, device, interleave: int = 0):
-        """`interleave` > 0 (two pieces of equal size, no bias): rows are stored in groups of `interleave` rows of the
+    def __init__(self, pieces: Sequence[Tuple[str, int]], in_features: int, bias: bool, dtype, device, interleave: int = 0,
+                 weight_suffix: str = ".weight", bias_suffix: str = ".bias"):
+        """The tensors are named `<prefix><weight_suffix>` and `<prefix><bias_suffix>`.  `interleave` > 0 (two pieces of equal size, no bias): rows are stored in groups of `interleave` rows of the
         first piece followed by the matching rows of the second, which is what a gated product reads."""
         self.interleave = interleave
+        self.weight_suffix, self.bias_suffix = weight_suffix, bias_suffix
         self.pieces = list(pieces)
         self.in_features = in_features
         self.out_features = sum(width for _, width in self.pieces)
@@ -39,9 +41,9 @@ class StackedLinear(Part):
     def tensor_specs(self):
         specs = {}
         for prefix, width in self.pieces:
-            specs[f"{prefix}.weight"] = TensorSpec((width, self.in_features), role="matrix")
+            specs[f"{prefix}{self.weight_suffix}"] = TensorSpec((width, self.in_features), role="matrix")
             if self.has_bias:
-                specs[f"{prefix}.bias"] = TensorSpec((width,), role="vector")
+                specs[f"{prefix}{self.bias_suffix}"] = TensorSpec((width,), role="vector")
         return specs
 
     def assign(self, name, tensor):
@@ -50,7 +52,7 @@ class StackedLinear(Part):
         self._parts[name] = tensor
 
     def finalize_weights(self):
-        weights = [self._parts.pop(f"{prefix}.weight") for prefix, _ in self.pieces]
+        weights = [self._parts.pop(f"{prefix}{self.weight_suffix}") for prefix, _ in self.pieces]
         if self.interleave:
             first, second = weights
             group, width = self.interleave, first.shape[1]
@@ -59,7 +61,7 @@ class StackedLinear(Part):
             self.weight = weights[0] if len(weights) == 1 else torch.cat(weights, dim=0).contiguous()
         del weights
         if self.has_bias:
-            biases = [self._parts.pop(f"{prefix}.bias") for prefix, _ in self.pieces]
+            biases = [self._parts.pop(f"{prefix}{self.bias_suffix}") for prefix, _ in self.pieces]
             self.bias = biases[0] if len(biases) == 1 else torch.cat(biases, dim=0).contiguous()
 
     def forward_gated(self, values):

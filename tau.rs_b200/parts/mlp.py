@@ -22,11 +22,13 @@ class SwiGLU(FeedForward):
         # Where the gated product exists (bfloat16, aligned sizes) gate and up rows are interleaved for it and the
         # activation is its epilogue; otherwise the two are stacked and the activation is a kernel of its own.
         self.fused = kernels.gated_fits(spec.hidden, spec.intermediate, dtype)
+        gate, up, down = (getattr(spec, key, default) for key, default in (("gate_name", "gate_proj"), ("up_name", "up_proj"), ("down_name", "down_proj")))
+        suffix = getattr(spec, "weight_suffix", ".weight")
         self.gate_up = StackedLinear(
-            [(f"{prefix}.gate_proj", spec.intermediate), (f"{prefix}.up_proj", spec.intermediate)],
-            spec.hidden, False, dtype, device, interleave=kernels.GATE_GROUP if self.fused else 0,
+            [(f"{prefix}.{gate}", spec.intermediate), (f"{prefix}.{up}", spec.intermediate)],
+            spec.hidden, False, dtype, device, interleave=kernels.GATE_GROUP if self.fused else 0, weight_suffix=suffix,
         )
-        self.down = StackedLinear([(f"{prefix}.down_proj", spec.hidden)], spec.intermediate, False, dtype, device)
+        self.down = StackedLinear([(f"{prefix}.{down}", spec.hidden)], spec.intermediate, False, dtype, device, weight_suffix=suffix)
 
     def tensor_specs(self):
         return {**self.gate_up.tensor_specs(), **self.down.tensor_specs()}

@@ -21,6 +21,7 @@ from .registry import build
 class DecoderModel:
     def __init__(self, spec: ModelSpec, dtype: torch.dtype, device):
         self.spec, self.dtype, self.device = spec, dtype, device
+        self.residual_dtype = torch.float32 if getattr(spec, "residual_dtype", None) == "float32" else dtype
         self.blocks = [build("block", block, dtype=dtype, device=device) for block in spec.blocks]
         self.final_norm = build("norm", spec.final_norm, name=spec.final_norm_name, dtype=dtype, device=device)
         self.input_position = None if spec.input_position is None else build("position", spec.input_position, device=device)
@@ -114,7 +115,7 @@ class DecoderModel:
     def forward(self, step, cache) -> Optional[torch.Tensor]:
         """Runs the step's tokens; returns 32-bit logits `[wanted, vocab]`, or None if nothing is wanted."""
         spec = self.spec
-        residual = torch.empty((step.n_tokens, spec.hidden), dtype=self.dtype, device=self.device)
+        residual = torch.empty((step.n_tokens, spec.hidden), dtype=self.residual_dtype, device=self.device)
         kernels.embedding(step.token_ids, self.embedding, residual)
         if self.input_position is not None:
             self.input_position.add_to(residual, step)

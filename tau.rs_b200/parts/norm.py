@@ -19,6 +19,7 @@ from .registry import register_norm
 class RMSNorm(Norm):
     def __init__(self, spec, name: str, dtype, device):
         self.spec, self.name = spec, name
+        self.dtype = dtype      # of the output; the input may be a residual stream kept in 32-bit
         self.weight = None
 
     def tensor_specs(self):
@@ -31,11 +32,11 @@ class RMSNorm(Norm):
 
     def forward(self, values, rows=None, branch=None):
         count = values.shape[0] if rows is None else rows.shape[0]
-        out = torch.empty((count, self.spec.width), dtype=values.dtype, device=values.device)
+        out = torch.empty((count, self.spec.width), dtype=self.dtype or values.dtype, device=values.device)
         kernels.rms_norm(values, self.weight, self.spec.eps, out, rows, branch)
         return out
 
     def add_forward(self, branch, residual):
-        out = torch.empty_like(residual)
+        out = torch.empty(residual.shape, dtype=self.dtype or residual.dtype, device=residual.device)
         kernels.add_rms_norm(branch, residual, self.weight, self.spec.eps, out)
         return out

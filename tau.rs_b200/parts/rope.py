@@ -43,3 +43,23 @@ class RotaryTables(Part):
         self.cos = torch.cos(angles).contiguous().to(self.device)
         self.sin = torch.sin(angles).contiguous().to(self.device)
         _TABLES[key] = (self.cos, self.sin)
+
+
+@register_position("rope_pairs")
+class PairRotation(Part):
+    """Rotation of neighbouring pairs: element `2i` with `2i + 1`, by the angle `position * theta^(-2i / rotary_dim)`.
+
+    Holds the frequencies alone (`inv_freq`, float32 `[rotary_dim / 2]`, the power taken in 64-bit and rounded once); the
+    kernels that rotate multiply them by the position and take sine and cosine in 32-bit themselves, so no table over
+    positions exists and no position is too large for one."""
+
+    def __init__(self, spec, device):
+        if spec.rotary_dim % 2 != 0 or spec.rotary_dim <= 0:
+            raise ValueError(f"rotary_dim must be a positive even number, found {spec.rotary_dim}")
+        self.spec, self.device = spec, device
+        self.inv_freq = None
+
+    def finalize_weights(self):
+        spec = self.spec
+        values = [float(spec.theta) ** (-2.0 * index / spec.rotary_dim) for index in range(spec.rotary_dim // 2)]
+        self.inv_freq = torch.tensor(values, dtype=torch.float64).to(torch.float32).to(self.device)

@@ -1,0 +1,91 @@
+"""Routed experts: each token passes `top` of `experts` gated feed-forwards, and optionally a shared one.
+
+    z = W_router h (32-bit);   s = sigmoid(z) (or softmax(z))
+    chosen = the `top` experts with the largest s + correction;   weights = s of the chosen (renormalised only if asked)
+    out = sum over chosen e of weight_e * W_down,e (silu(W_gate,e h) * (W_up,e h))  +  sigmoid(w_sg . h) * shared(h)
+
+The router, the choice and the weighted sum are 32-bit, and so is the output.  The experts' weights are stacked
+(`[experts, 2 I, width]` gate rows then up rows, `[experts, width, I]`), nothing travels to the host, and the kernels index
+the experts by the router's choice on the device, so a decode step through this part is captured in a graph like any other.
+A step reads only the experts that its tokens chose, which `bytes_read_per_step` accounts for.  Tensor names under the
+prefix: `router`, `correction`, `e<j>.gate`, `e<j>.up`, `e<j>.down`, `shared.gate|up|down`, `shared.sg`.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..csrc import kernels
+from ..weights.tensor_spec import TensorSpec
+from .base import FeedForward
+from .registry import build, register_feed_forward
+
+
+@register_feed_forward("routed_experts")
+class RoutedExperts(FeedForward):
+    def __init__(self, spec, prefix: str, dtype, device):
+        if spec.score not in ("sigmoid", "softmax"):
+            raise ValueError(f"unknown router score {spec.score!r}")
+        if not 1 <= spec.top <= spec.experts:
+            raise ValueError("top must lie between 1 and the number of experts")
+        if spec.shared_gate and spec.shared is None:
+            raise ValueError("a shared gate needs a shared expert")
+        self.spec, self.prefix, self.dtype = spec, prefix, dtype
+        self.shared = None if spec.shared is None else build("feed_forward", spec.shared, prefix=f"{prefix}.shared", dtype=dtype, device=device)
+        self._own = {f"{prefix}.router": TensorSpec((spec.experts, spec.hidden), role="vector")}
+        if spec.correction:
+            self._own[f"{prefix}.correction"] = TensorSpec((spec.experts,), role="vector")
+        if spec.shared_gate:
+            self._own[f"{prefix}.shared.sg"] = TensorSpec((1, spec.hidden), role="vector")
+        for expert in range(spec.experts):
+            self._own[f"{prefix}.e{expert}.gate"] = TensorSpec((spec.intermediate, spec.hidden), role="matrix")
+            self._own[f"{prefix}.e{expert}.up"] = TensorSpec((spec.intermediate, spec.hidden), role="matrix")
+            self._own[f"{prefix}.e{expert}.down"] = TensorSpec((spec.hidden, spec.intermediate), role="matrix")
+        self._held = {}
+        self.router = self.correction = self.shared_gate = self.gate_up = self.down = None
+
+    def tensor_specs(self):
+        specs = dict(self._own)
+        if self.shared is not None:
+            specs.update(self.shared.tensor_specs())
+        return specs
+
+    def assign(self, name, tensor):
+        if name in self._own:
+            self._held[name] = tensor
+        elif self.shared is not None:
+            self.shared.assign(name, tensor)
+        else:
+            raise KeyError(name)
+
+    def finalize_weights(self):
+        spec, prefix, held = self.spec, self.prefix, self._held
+        if self.shared is not None:
+            self.shared.finalize_weights()
+        self.router = held.pop(f"{prefix}.router")
+        self.correction = held.pop(f"{prefix}.correction") if spec.correction else None
+        self.shared_gate = held.pop(f"{prefix}.shared.sg").reshape(-1).contiguous() if spec.shared_gate else None
+        self.gate_up = torch.stack([torch.cat([held.pop(f"{prefix}.e{e}.gate"), held.pop(f"{prefix}.e{e}.up")], dim=0) for e in range(spec.experts)])
+        self.down = torch.stack([held.pop(f"{prefix}.e{e}.down") for e in range(spec.experts)])
+
+    def bytes_read_per_step(self, dtype) -> int:
+        """The router, the shared expert and `top` experts: what a step of one token reads (more tokens read more experts,
+        at most all of them)."""
+        spec = self.spec
+        element = torch.empty((), dtype=dtype).element_size()
+        total = spec.experts * spec.hidden * 4 + spec.top * 3 * spec.intermediate * spec.hidden * element
+        return total + (self.shared.bytes_read_per_step(dtype) if self.shared is not None else 0)
+
+    def forward(self, hidden, step):
+        spec = self.spec
+        tokens, device = hidden.shape[0], hidden.device
+        chosen = torch.empty((tokens, spec.top), dtype=torch.int32, device=device)
+        weights = torch.empty((tokens, spec.top), dtype=torch.float32, device=device)
+        shared_gate = torch.empty((tokens,), dtype=torch.float32, device=device) if spec.shared_gate else None
+        kernels.moe_route(hidden, self.router, self.correction, self.shared_gate, chosen, weights, shared_gate, spec.top,
+                          spec.score == "softmax", spec.renormalize)
+        inner = torch.empty((tokens, spec.top, spec.intermediate), dtype=hidden.dtype, device=device)
+        kernels.moe_gate_up(hidden, self.gate_up, chosen, inner)
+        shared_out = None if self.shared is None else self.shared.forward(hidden, step)
+        out = torch.empty((tokens, spec.hidden), dtype=torch.float32, device=device)
+        kernels.moe_down(inner, self.down, chosen, weights, shared_out, shared_gate, out)
+        return out
