@@ -270,6 +270,108 @@ def our_kernel_times(torch, kernels, config, batch):
     return times
 
 
+def fasesun_sizes():
+    """Layer sizes that resemble real models of the kinds of layer Fasesun mixes, and for each a dense Qwen3 of the same width,
+    depth and vocabulary whose feed-forward is as wide as the experts that one token passes (chosen ones and the shared one)."""
+    def fasesun(width, heads, q_rank, memory_heads, expert_ff, shared_ff, experts=64, top=6):
+        moe = {"kind": "moe", "router": {"experts": experts, "top": top}, "expert": {"ff": expert_ff}, "shared": {"ff": shared_ff}}
+        latent = {"type": "latent_attention", "mlp": moe, "mixer": {"heads": heads, "dim": 128, "rot_dim": 64, "vdim": 128, "q_rank": q_rank, "kv_rank": 512,
+                                                                    "scale": 192 ** -0.5, "rot": {"base": 10000.0, "dims": 64}}}
+        memory = {"type": "mlstm", "mlp": moe, "mixer": {"heads": memory_heads, "dim": 256, "vdim": 512, "gate_cap": 15.0}}
+        decaying = {"type": "lightning", "mlp": moe, "mixer": {"heads": heads, "dim": 128, "vdim": 128, "decay": [1.0 - 2.0 ** (-5 - 3 * h / heads) for h in range(heads)]}}
+        return {"architecture": "Fasesun", "layers": [latent, memory, decaying, memory], "norm": {"eps": 1e-5}, "vocab": 32768, "width": width}
+
+    def dense(width, heads, intermediate):
+        return dict(qwen3(4, width, heads, 8, intermediate, True), vocab_size=32768)
+
+    return {
+        "2048": (fasesun(2048, 16, 768, 4, 1408, 2816), dense(2048, 16, 6 * 1408 + 2816)),
+        "4096": (fasesun(4096, 32, 1536, 8, 2048, 4096), dense(4096, 32, 6 * 2048 + 4096)),
+    }
+
+
+def design_comparison(args) -> int:
+    """`--design fasesun`: prefill and decode throughput of Fasesun layers at two real sizes beside a dense Qwen3 of equal width,
+    depth and active feed-forward width, with the device time of each kernel class in one prompt step and one decode step."""
+    import numpy as np
+    import torch
+
+    import tau_rs_b200
+    from tau_rs_b200 import Engine, StepEntry
+    from tau_rs_b200.csrc import kernels
+
+    torch.cuda.set_device(0)
+    peaks = measured_peaks()
+    batch, context, steps = args.batch or 8, args.context or 2048, args.steps or 32
+    rng = np.random.default_rng(0)
+    records = []
+    clocks = ClockSampler()
+    clocks.start()
+    for size, (design_config, dense_config) in fasesun_sizes().items():
+        record = {"size": size, "batch": batch, "context": context}
+        for label, config in (("fasesun", design_config), ("qwen3", dense_config)):
+            model = tau_rs_b200.random_model(config, seed=0, dtype="bfloat16", device="cuda:0")
+            vocab = model.spec.vocab_size
+            engine = Engine(model, max_tokens=batch * (context + 256), max_sequence_tokens=context + 256)
+
+            def timed(function):
+                start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                torch.cuda.synchronize()
+                start.record()
+                function()
+                stop.record()
+                torch.cuda.synchronize()
+                return start.elapsed_time(stop)
+
+            def prefill_once(classes=False):
+                slot = engine.open_sequence()
+                tokens = rng.integers(0, vocab, size=context).tolist()
+                if classes:
+                    torch.cuda.synchronize()
+                    kernels.start_timing()
+                engine.step([StepEntry(slot, tokens, [context - 1])])
+                per_class = kernels.take_timing(stop=True) if classes else None
+                engine.close_sequence(slot)
+                return per_class
+
+            for _ in range(3):
+                prefill_once()
+            prefill_ms = min(timed(prefill_once) for _ in range(3))
+            prefill_classes = prefill_once(classes=True)
+            slots = [engine.open_sequence() for _ in range(batch)]
+            engine.step([StepEntry(slot, rng.integers(0, vocab, size=context).tolist(), []) for slot in slots])
+
+            def decode_once():
+                engine.step([StepEntry(slot, [int(rng.integers(0, vocab))], [0]) for slot in slots])
+
+            for _ in range(max(3, args.warmup)):
+                decode_once()
+            torch.cuda.synchronize()
+            time.sleep(0.3)
+            decode_ms = timed(lambda: [decode_once() for _ in range(steps)]) / steps
+            engine.use_graphs = False
+            decode_once()
+            torch.cuda.synchronize()
+            kernels.start_timing()
+            decode_once()
+            decode_classes = kernels.take_timing(stop=True)
+            read = engine.bytes_read_by_a_decode_step()
+            record[label] = {
+                "prefill_tok_s": round(context / prefill_ms * 1e3, 1), "prefill_ms": round(prefill_ms, 3),
+                "decode_tok_s": round(batch / decode_ms * 1e3, 1), "decode_ms_per_step": round(decode_ms, 4),
+                "decode_bytes_per_step": read, "decode_frac_of_copy_bandwidth": round(read / (decode_ms * 1e-3) / (peaks["hbm_gbs"] * 1e9), 4),
+                "prefill_ms_by_class": prefill_classes, "decode_ms_by_class": decode_classes,
+            }
+            for slot in slots:
+                engine.close_sequence(slot)
+            del engine, model
+            torch.cuda.empty_cache()
+        records.append(record)
+    print(json.dumps({"design": "fasesun", "beside": "qwen3 of equal width, depth and active feed-forward width", "dtype": "bf16", "data": "synthetic",
+                      "peaks": peaks, "sizes": records, "clocks": clocks.stop()}))
+    return 0
+
+
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -285,8 +387,12 @@ def main() -> int:
     parser.add_argument("--sections", default="prefill,decode,points,e2e",
                         help="which measurements to run: prefill, decode, points, e2e, kernels (the counterparts of the reference arm's kernels), "
                              "classes (time per kernel class of a decode step, outside a graph)")
+    parser.add_argument("--design", default="", choices=["", "fasesun"],
+                        help="instead of the default workload: layers of this design at real sizes beside a dense Qwen3 of equal size")
     args = parser.parse_args()
 
+    if args.design:
+        return design_comparison(args)
     if args.gpus != 1:
         print(f"bench.py measures one GPU; --gpus {args.gpus} is not supported by this single-GPU library")
         return 2

@@ -83,7 +83,8 @@ _CLASS_OF = {
     "attention_decode": "attention", "attention_prefill": "attention", "attention_prefill_tc": "attention", "argmax": "selection",
     "sample_gumbel": "selection", "store_words_host": "selection", "random_normal": "other",
     "stream_add_norm": "norm", "gated_group_norm": "norm", "gemm_simt_batched": "product", "linear_recurrence": "recurrence",
-    "latent_prepare": "attention", "latent_attention": "attention", "moe_route": "routing", "moe_gate_up": "product", "moe_down": "product",
+    "latent_prepare": "attention", "latent_attention": "attention", "moe_route": "routing", "moe_gate_up": "product", "moe_down": "product", "moe_sort": "routing", "moe_gather": "routing",
+    "moe_combine": "routing",
 }
 _timing = None     # while timing: [last event, [(class, event after the launch), ...]]
 
@@ -768,7 +769,6 @@ def linear_recurrence(q, k, v, gates, decays, state, cu_seqlens, seq_slot, out, 
     if exponential:
         _require(gates is not None and gates.shape == (tokens, 2 * n_heads) and gates.dtype == torch.float32 and gates.is_contiguous(),
                  "gates must be float32 [tokens, 2 * heads]")
-        _require(value_dim + 1 <= 128, "with exponential gating a head may have at most 127 value elements")
     else:
         _f32_vector(decays, n_heads, "the decays")
         _require(decays is not None, "decays are needed")
@@ -809,9 +809,11 @@ def moe_route(hidden, router, correction, shared_gate_weight, chosen, weights, s
                                  _stream()), "moe_route")
 
 
-def moe_gate_up(hidden, gate_up, chosen, inner) -> None:
+def moe_gate_up(hidden, gate_up, chosen, inner, interleave: int = 0) -> None:
     """`inner[token, place] = silu(gate_e @ h) * (up_e @ h)` with `e = chosen[token, place]`; `gate_up` [experts, 2 * I, width]
-    holds each expert's gate rows, then its up rows; `inner` [tokens, top, I]."""
+    holds each expert's gate rows, then its up rows, or with `interleave` groups of that many gate rows each followed by
+    their up rows (what `linear_gated` reads); `inner` [tokens, top, I]."""
+    _require(interleave == 0 or inner.shape[2] % interleave == 0, "the interleaved groups must divide the expert's width")
     _on_device(hidden, gate_up, chosen, inner)
     tokens, width = hidden.shape
     top, size = inner.shape[1], inner.shape[2]
@@ -821,7 +823,7 @@ def moe_gate_up(hidden, gate_up, chosen, inner) -> None:
              and chosen.is_contiguous(), "shapes must be [T,W], [E,2I,W], [T,top] -> [T,top,I]")
     library = build.load_library("moe.cu")
     _check(library.tau_moe_gate_up(_code(hidden), _pointer(hidden), _pointer(gate_up), _pointer(chosen), _pointer(inner), ctypes.c_int(tokens),
-                                   ctypes.c_int(width), ctypes.c_int(size), ctypes.c_int(top), _stream()), "moe_gate_up")
+                                   ctypes.c_int(width), ctypes.c_int(size), ctypes.c_int(top), ctypes.c_int(interleave), _stream()), "moe_gate_up")
 
 
 def moe_down(inner, down, chosen, weights, shared_out, shared_gate, out) -> None:
@@ -843,6 +845,48 @@ def moe_down(inner, down, chosen, weights, shared_out, shared_gate, out) -> None
     _check(library.tau_moe_down(_code(inner), _pointer(inner), _pointer(down), _pointer(chosen), _pointer(weights), _pointer(shared_out),
                                 _pointer(shared_gate), _pointer(out), ctypes.c_int(tokens), ctypes.c_int(width), ctypes.c_int(size), ctypes.c_int(top),
                                 _stream()), "moe_down")
+
+
+def moe_sort(chosen, experts: int, offsets, order, position) -> None:
+    """Groups the (token, place) pairs of `chosen` [tokens, top] by expert: `order` lists the pairs expert by expert,
+    `offsets` [experts + 1] bounds each expert's part of it, `position[pair]` is where a pair went (all int32)."""
+    _on_device(chosen, offsets, order, position)
+    pairs = chosen.numel()
+    _require(chosen.dtype == torch.int32 and chosen.is_contiguous(), "chosen must be contiguous int32")
+    for tensor, count, what in ((offsets, experts + 1, "offsets"), (order, pairs, "order"), (position, pairs, "position")):
+        _require(tensor.dtype == torch.int32 and tensor.numel() == count and tensor.is_contiguous(), f"{what} must be int32 of {count} elements")
+    library = build.load_library("moe.cu")
+    _check(library.tau_moe_sort(_pointer(chosen), ctypes.c_int(pairs), ctypes.c_int(experts), _pointer(offsets), _pointer(order), _pointer(position),
+                                _stream()), "moe_sort")
+
+
+def moe_gather(hidden, order, top: int, gathered) -> None:
+    """`gathered[i] = hidden[order[i] // top]`."""
+    _on_device(hidden, order, gathered)
+    pairs, width = gathered.shape
+    _require(hidden.is_contiguous() and gathered.is_contiguous() and hidden.dtype == gathered.dtype and hidden.shape[1] == width
+             and order.dtype == torch.int32 and order.numel() == pairs, "gathered must be [pairs, width] of the input's dtype")
+    library = build.load_library("moe.cu")
+    _check(library.tau_moe_gather(_code(hidden), _pointer(hidden), _pointer(order), _pointer(gathered), ctypes.c_int(pairs), ctypes.c_int(width),
+                                  ctypes.c_int(top), _stream()), "moe_gather")
+
+
+def moe_combine(rows, position, weights, shared_out, shared_gate, out) -> None:
+    """`out[token] = sum_place weights[token, place] * rows[position[token, place]] + shared_gate[token] * shared_out[token]`;
+    `rows` float32 [pairs, width], `out` float32 [tokens, width]."""
+    _on_device(rows, position, weights, shared_out, shared_gate, out)
+    tokens, width = out.shape
+    top = weights.shape[1]
+    _require(rows.dtype == torch.float32 == out.dtype and rows.shape == (tokens * top, width) and rows.is_contiguous() and out.is_contiguous(),
+             "rows must be float32 [tokens * top, width]")
+    _require(position.dtype == torch.int32 and position.numel() == tokens * top and weights.dtype == torch.float32 and weights.is_contiguous(),
+             "one position and one weight per pair")
+    if shared_out is not None:
+        _require(shared_out.shape == (tokens, width) and shared_out.is_contiguous(), "the shared output must be [tokens, width]")
+    library = build.load_library("moe.cu")
+    _check(library.tau_moe_combine(_code(shared_out) if shared_out is not None else 0, _pointer(rows), _pointer(position), _pointer(weights),
+                                   _pointer(shared_out), _pointer(shared_gate), _pointer(out), ctypes.c_int(tokens), ctypes.c_int(width),
+                                   ctypes.c_int(top), _stream()), "moe_combine")
 
 
 # ---------------------------------------------------------------------------- random weights

@@ -23,6 +23,26 @@ __device__ __forceinline__ float warp_dot(const T* __restrict__ weights, const f
     return warp_sum(sum);
 }
 
+// bfloat16 rows that start on a 16-byte boundary are read eight elements at a time.
+template <>
+__device__ __forceinline__ float warp_dot<bf16>(const bf16* __restrict__ weights, const float* __restrict__ vector, int length, int lane) {
+    float sum = 0.0f;
+    if ((reinterpret_cast<uintptr_t>(weights) & 15) == 0 && length % 8 == 0) {
+        for (int column = lane * 8; column < length; column += 256) {
+            const uint4 raw = *reinterpret_cast<const uint4*>(weights + column);
+            const unsigned words[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                sum = fmaf(__uint_as_float(words[i] << 16), vector[column + 2 * i], sum);
+                sum = fmaf(__uint_as_float(words[i] & 0xffff0000u), vector[column + 2 * i + 1], sum);
+            }
+        }
+    } else {
+        for (int column = lane; column < length; column += 32) sum = fmaf(__bfloat162float(weights[column]), vector[column], sum);
+    }
+    return warp_sum(sum);
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kThreads)
 moe_route_kernel(const T* __restrict__ hidden, const float* __restrict__ router, const float* __restrict__ correction,
@@ -91,7 +111,7 @@ moe_route_kernel(const T* __restrict__ hidden, const float* __restrict__ router,
 template <typename T>
 __global__ void __launch_bounds__(kThreads)
 moe_gate_up_kernel(const T* __restrict__ hidden, const T* __restrict__ gate_up, const int* __restrict__ chosen, T* __restrict__ inner_out,
-                   int width, int inner, int top, int features_per_block) {
+                   int width, int inner, int top, int features_per_block, int interleave) {
     grid_dependents_launch();
     grid_dependency_wait();
     extern __shared__ float row[];
@@ -101,8 +121,11 @@ moe_gate_up_kernel(const T* __restrict__ hidden, const T* __restrict__ gate_up, 
     const T* weights = gate_up + static_cast<size_t>(chosen[pair]) * 2 * inner * width;
     const int begin = blockIdx.y * features_per_block, end = min(inner, begin + features_per_block);
     for (int feature = begin + warp; feature < end; feature += kWarps) {
-        const float gate = warp_dot(weights + static_cast<size_t>(feature) * width, row, width, lane);
-        const float up = warp_dot(weights + static_cast<size_t>(inner + feature) * width, row, width, lane);
+        // Plain: gate rows, then up rows.  Interleaved: groups of `interleave` gate rows, each followed by its up rows.
+        const int gate_row = interleave ? feature / interleave * 2 * interleave + feature % interleave : feature;
+        const int up_row = interleave ? gate_row + interleave : inner + feature;
+        const float gate = warp_dot(weights + static_cast<size_t>(gate_row) * width, row, width, lane);
+        const float up = warp_dot(weights + static_cast<size_t>(up_row) * width, row, width, lane);
         if (lane == 0) inner_out[static_cast<size_t>(pair) * inner + feature] = from_float<T>(gate / (1.0f + expf(-gate)) * up);
     }
 }
@@ -133,6 +156,61 @@ moe_down_kernel(const T* __restrict__ inner_in, const T* __restrict__ down, cons
     }
 }
 
+// The (token, place) pairs grouped by expert, by one block: offsets[e] .. offsets[e + 1] are the places of expert e's pairs in
+// `order`; position[pair] is where a pair went.  The order inside a group depends on timing; nothing computed from it does.
+__global__ void __launch_bounds__(1024)
+moe_sort_kernel(const int* __restrict__ chosen, int pairs, int experts, int* __restrict__ offsets, int* __restrict__ order, int* __restrict__ position) {
+    grid_dependents_launch();
+    grid_dependency_wait();
+    extern __shared__ int counters[];       // [experts] counts, then [experts] cursors
+    int* cursor = counters + experts;
+    for (int expert = threadIdx.x; expert < experts; expert += blockDim.x) counters[expert] = 0;
+    __syncthreads();
+    for (int pair = threadIdx.x; pair < pairs; pair += blockDim.x) atomicAdd(&counters[chosen[pair]], 1);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int total = 0;
+        for (int expert = 0; expert < experts; ++expert) {
+            offsets[expert] = total;
+            cursor[expert] = total;
+            total += counters[expert];
+        }
+        offsets[experts] = total;
+    }
+    __syncthreads();
+    for (int pair = threadIdx.x; pair < pairs; pair += blockDim.x) {
+        const int place = atomicAdd(&cursor[chosen[pair]], 1);
+        order[place] = pair;
+        position[pair] = place;
+    }
+}
+
+// gathered[i] = hidden[order[i] / top]: the rows of each expert's tokens side by side.
+template <typename T>
+__global__ void moe_gather_kernel(const T* __restrict__ hidden, const int* __restrict__ order, T* __restrict__ gathered, int width, int top) {
+    grid_dependents_launch();
+    grid_dependency_wait();
+    const T* source = hidden + static_cast<size_t>(order[blockIdx.x] / top) * width;
+    T* target = gathered + static_cast<size_t>(blockIdx.x) * width;
+    for (int column = threadIdx.x; column < width; column += blockDim.x) target[column] = source[column];
+}
+
+// out[token] = sum over places of weight * rows[position[token, place]] + shared_gate * shared[token], in place order.
+template <typename T>
+__global__ void moe_combine_kernel(const float* __restrict__ rows, const int* __restrict__ position, const float* __restrict__ weights,
+                                   const T* __restrict__ shared_out, const float* __restrict__ shared_gate, float* __restrict__ out, int width, int top) {
+    grid_dependents_launch();
+    grid_dependency_wait();
+    const int token = blockIdx.x;
+    for (int column = threadIdx.x; column < width; column += blockDim.x) {
+        float sum = 0.0f;
+        for (int place = 0; place < top; ++place)
+            sum = fmaf(weights[static_cast<size_t>(token) * top + place], rows[static_cast<size_t>(position[static_cast<size_t>(token) * top + place]) * width + column], sum);
+        if (shared_out) sum += (shared_gate ? shared_gate[token] : 1.0f) * to_float(shared_out[static_cast<size_t>(token) * width + column]);
+        out[static_cast<size_t>(token) * width + column] = sum;
+    }
+}
+
 template <typename T>
 int launch_all(int what, const void* a, const void* b, const void* c, const void* d, const void* e, const void* f, void* o1, void* o2, void* o3,
                int tokens, int width, int inner, int experts, int top, int flag_a, int flag_b, cudaStream_t s) {
@@ -148,7 +226,7 @@ int launch_all(int what, const void* a, const void* b, const void* c, const void
         if (bytes > 48 * 1024 && cudaFuncSetAttribute(moe_gate_up_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes)) != cudaSuccess)
             return cudaErrorInvalidValue;
         tau_launch(moe_gate_up_kernel<T>, dim3(tokens * top, (inner + per_block - 1) / per_block), dim3(kThreads), bytes, s, static_cast<const T*>(a),
-                   static_cast<const T*>(b), static_cast<const int*>(c), static_cast<T*>(o1), width, inner, top, per_block);
+                   static_cast<const T*>(b), static_cast<const int*>(c), static_cast<T*>(o1), width, inner, top, per_block, flag_a);
     } else {
         const int per_block = 64;
         const size_t bytes = static_cast<size_t>(top) * inner * sizeof(float);
@@ -175,12 +253,12 @@ TAU_EXPORT int tau_moe_route(int dtype, const void* hidden, const float* router,
 }
 
 TAU_EXPORT int tau_moe_gate_up(int dtype, const void* hidden, const void* gate_up, const int* chosen, void* inner_out, int tokens, int width, int inner,
-                               int top, void* stream) {
+                               int top, int interleave, void* stream) {
     if (tokens <= 0) return 0;
     if (!hidden || !gate_up || !chosen || !inner_out || width <= 0 || inner <= 0 || top <= 0 || static_cast<long long>(tokens) * top > 0x7fffffff) return cudaErrorInvalidValue;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (dtype == TAU_F32) return launch_all<float>(1, hidden, gate_up, chosen, nullptr, nullptr, nullptr, inner_out, nullptr, nullptr, tokens, width, inner, 0, top, 0, 0, s);
-    if (dtype == TAU_BF16) return launch_all<bf16>(1, hidden, gate_up, chosen, nullptr, nullptr, nullptr, inner_out, nullptr, nullptr, tokens, width, inner, 0, top, 0, 0, s);
+    if (dtype == TAU_F32) return launch_all<float>(1, hidden, gate_up, chosen, nullptr, nullptr, nullptr, inner_out, nullptr, nullptr, tokens, width, inner, 0, top, interleave, 0, s);
+    if (dtype == TAU_BF16) return launch_all<bf16>(1, hidden, gate_up, chosen, nullptr, nullptr, nullptr, inner_out, nullptr, nullptr, tokens, width, inner, 0, top, interleave, 0, s);
     return cudaErrorInvalidValue;
 }
 
@@ -192,4 +270,33 @@ TAU_EXPORT int tau_moe_down(int dtype, const void* inner_in, const void* down, c
     if (dtype == TAU_F32) return launch_all<float>(2, inner_in, down, chosen, weights, shared_out, shared_gate, out, nullptr, nullptr, tokens, width, inner, 0, top, 0, 0, s);
     if (dtype == TAU_BF16) return launch_all<bf16>(2, inner_in, down, chosen, weights, shared_out, shared_gate, out, nullptr, nullptr, tokens, width, inner, 0, top, 0, 0, s);
     return cudaErrorInvalidValue;
+}
+
+TAU_EXPORT int tau_moe_sort(const int* chosen, int pairs, int experts, int* offsets, int* order, int* position, void* stream) {
+    if (pairs <= 0) return 0;
+    if (!chosen || !offsets || !order || !position || experts <= 0 || experts > 4096) return cudaErrorInvalidValue;
+    tau_launch(moe_sort_kernel, dim3(1), dim3(1024), static_cast<size_t>(2 * experts) * sizeof(int), static_cast<cudaStream_t>(stream), chosen, pairs, experts,
+               offsets, order, position);
+    return tau_launch_status();
+}
+
+TAU_EXPORT int tau_moe_gather(int dtype, const void* hidden, const int* order, void* gathered, int pairs, int width, int top, void* stream) {
+    if (pairs <= 0) return 0;
+    if (!hidden || !order || !gathered || width <= 0 || top <= 0) return cudaErrorInvalidValue;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (dtype == TAU_F32) tau_launch(moe_gather_kernel<float>, dim3(pairs), dim3(kThreads), 0, s, static_cast<const float*>(hidden), order, static_cast<float*>(gathered), width, top);
+    else if (dtype == TAU_BF16) tau_launch(moe_gather_kernel<bf16>, dim3(pairs), dim3(kThreads), 0, s, static_cast<const bf16*>(hidden), order, static_cast<bf16*>(gathered), width, top);
+    else return cudaErrorInvalidValue;
+    return tau_launch_status();
+}
+
+TAU_EXPORT int tau_moe_combine(int dtype, const float* rows, const int* position, const float* weights, const void* shared_out, const float* shared_gate,
+                               float* out, int tokens, int width, int top, void* stream) {
+    if (tokens <= 0) return 0;
+    if (!rows || !position || !weights || !out || width <= 0 || top <= 0) return cudaErrorInvalidValue;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (dtype == TAU_F32) tau_launch(moe_combine_kernel<float>, dim3(tokens), dim3(kThreads), 0, s, rows, position, weights, static_cast<const float*>(shared_out), shared_gate, out, width, top);
+    else if (dtype == TAU_BF16) tau_launch(moe_combine_kernel<bf16>, dim3(tokens), dim3(kThreads), 0, s, rows, position, weights, static_cast<const bf16*>(shared_out), shared_gate, out, width, top);
+    else return cudaErrorInvalidValue;
+    return tau_launch_status();
 }

@@ -24,7 +24,7 @@ namespace {
 constexpr int kDim = TAU_KEY_DIM;
 constexpr int kSplit = kDim <= 64 ? 1 : kDim <= 128 ? 2 : kDim <= 256 ? 4 : 8;   // threads that share a column
 constexpr int kRows = (kDim + kSplit - 1) / kSplit;                               // key rows per thread
-constexpr int kColumns = 128;                                                     // columns of a block (n included)
+constexpr int kColumns = 32;                                                      // columns of a block (n included)
 
 __device__ __forceinline__ float activate(float value, int activation) { return activation ? value / (1.0f + expf(-value)) : value; }
 
@@ -38,11 +38,15 @@ linear_recurrence_kernel(const T* __restrict__ q, const T* __restrict__ k, const
     grid_dependency_wait();
     __shared__ float qs[kDim], ks[kDim], partial[kSplit][kColumns], scalars[4];
     const int head = blockIdx.x, sequence = blockIdx.y;
-    const int columns = value_dim + (exponential ? 1 : 0);           // n rides as one more column
-    const int column = blockIdx.z * kColumns + threadIdx.x % kColumns;
+    const int columns = value_dim + (exponential ? 1 : 0);           // n rides as one more column of the state
+    // A block serves a tile of value columns; with the exponential gating its last thread column serves n as well, in every
+    // block (each needs n . q), and the first block alone writes n and m back.
+    const int tile = exponential ? kColumns - 1 : kColumns;
+    const int local = threadIdx.x % kColumns;
+    const bool is_n = exponential && local == kColumns - 1;
+    const int column = is_n ? value_dim : blockIdx.z * tile + local;
     const int part = threadIdx.x / kColumns, row0 = part * kRows;
-    const bool live = column < columns;
-    const bool is_n = exponential && column == value_dim;
+    const bool live = is_n || column < value_dim;
     float* record = state + static_cast<size_t>(seq_slot[sequence]) * slot_stride + static_cast<size_t>(head) * (static_cast<size_t>(columns) * kDim + (exponential ? 1 : 0));
     float S[kRows];
 #pragma unroll
@@ -92,7 +96,7 @@ linear_recurrence_kernel(const T* __restrict__ q, const T* __restrict__ k, const
         if (live && !is_n && part == 0) out[static_cast<size_t>(token) * heads * value_dim + head * value_dim + column] = sum;
         __syncthreads();    // qs, ks, partial and scalars are written again for the next token
     }
-    if (live) {
+    if (live && (!is_n || blockIdx.z == 0)) {
 #pragma unroll
         for (int r = 0; r < kRows; ++r)
             if (row0 + r < kDim) record[static_cast<size_t>(column) * kDim + row0 + r] = S[r];
@@ -113,11 +117,9 @@ TAU_EXPORT int tau_linear_recurrence(int dtype, const void* q, const void* k, co
     if (n_seqs <= 0) return 0;
     if (!q || !k || !v || !state || !cu_seqlens || !seq_slot || !out || heads <= 0 || value_dim <= 0 || (exponential ? !gates : !decays))
         return cudaErrorInvalidValue;
-    // With the exponential gating every block needs the n column; the tiles after the first would not have it.
-    const int columns = value_dim + (exponential ? 1 : 0);
-    if (exponential && columns > kColumns) return cudaErrorInvalidValue;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    dim3 grid(heads, n_seqs, (columns + kColumns - 1) / kColumns), block(kColumns * kSplit);
+    const int tile = exponential ? kColumns - 1 : kColumns;
+    dim3 grid(heads, n_seqs, (value_dim + tile - 1) / tile), block(kColumns * kSplit);
     if (dtype == TAU_F32)
         tau_launch(linear_recurrence_kernel<float>, grid, block, 0, s, static_cast<const float*>(q), static_cast<const float*>(k), static_cast<const float*>(v),
                    stride, gates, decays, state, slot_stride, cu_seqlens, seq_slot, out, heads, value_dim, exponential, gate_cap, query_scale, activation);

@@ -5,8 +5,16 @@
     out = sum over chosen e of weight_e * W_down,e (silu(W_gate,e h) * (W_up,e h))  +  sigmoid(w_sg . h) * shared(h)
 
 The router, the choice and the weighted sum are 32-bit, and so is the output.  The experts' weights are stacked
-(`[experts, 2 I, width]` gate rows then up rows, `[experts, width, I]`), nothing travels to the host, and the kernels index
-the experts by the router's choice on the device, so a decode step through this part is captured in a graph like any other.
+(`[experts, 2 I, width]`, `[experts, width, I]`).  Two ways through the experts:
+
+* few tokens (every decode step, and all of float32): weight-streaming kernels that index the experts by the router's choice
+  on the device; nothing travels to the host, so a decode step through this part is captured in a graph like any other;
+* runs of new tokens in bfloat16 (`GROUPED_FROM` pairs or more): the (token, place) pairs are grouped by expert on the
+  device, each expert's rows pass through the tensor-core products that dense feed-forwards use (gate and up as one gated
+  product), and a last kernel sums each token's places in place order.  The host reads the experts' row counts for this
+  (one small copy per layer), which a prompt's step can afford and a captured decode step could not.
+
+Both compute the same sums in 32-bit from the same roundings of the inputs; they differ as two product kernels differ.
 A step reads only the experts that its tokens chose, which `bytes_read_per_step` accounts for.  Tensor names under the
 prefix: `router`, `correction`, `e<j>.gate`, `e<j>.up`, `e<j>.down`, `shared.gate|up|down`, `shared.sg`.
 """
@@ -18,6 +26,9 @@ from ..csrc import kernels
 from ..weights.tensor_spec import TensorSpec
 from .base import FeedForward
 from .registry import build, register_feed_forward
+
+
+GROUPED_FROM = 512    # (token, place) pairs from which a run of new tokens takes the grouped products
 
 
 @register_feed_forward("routed_experts")
@@ -40,6 +51,8 @@ class RoutedExperts(FeedForward):
             self._own[f"{prefix}.e{expert}.gate"] = TensorSpec((spec.intermediate, spec.hidden), role="matrix")
             self._own[f"{prefix}.e{expert}.up"] = TensorSpec((spec.intermediate, spec.hidden), role="matrix")
             self._own[f"{prefix}.e{expert}.down"] = TensorSpec((spec.hidden, spec.intermediate), role="matrix")
+        # Where the gated product exists the experts' gate and up rows are interleaved for it (as a dense feed-forward's are).
+        self.interleave = kernels.GATE_GROUP if kernels.gated_fits(spec.hidden, spec.intermediate, dtype) else 0
         self._held = {}
         self.router = self.correction = self.shared_gate = self.gate_up = self.down = None
 
@@ -64,7 +77,14 @@ class RoutedExperts(FeedForward):
         self.router = held.pop(f"{prefix}.router")
         self.correction = held.pop(f"{prefix}.correction") if spec.correction else None
         self.shared_gate = held.pop(f"{prefix}.shared.sg").reshape(-1).contiguous() if spec.shared_gate else None
-        self.gate_up = torch.stack([torch.cat([held.pop(f"{prefix}.e{e}.gate"), held.pop(f"{prefix}.e{e}.up")], dim=0) for e in range(spec.experts)])
+        group = self.interleave
+
+        def stacked(gate, up):
+            if not group:
+                return torch.cat([gate, up], dim=0)
+            return torch.stack([gate.view(-1, group, spec.hidden), up.view(-1, group, spec.hidden)], dim=1).reshape(-1, spec.hidden)
+
+        self.gate_up = torch.stack([stacked(held.pop(f"{prefix}.e{e}.gate"), held.pop(f"{prefix}.e{e}.up")) for e in range(spec.experts)])
         self.down = torch.stack([held.pop(f"{prefix}.e{e}.down") for e in range(spec.experts)])
 
     def bytes_read_per_step(self, dtype) -> int:
@@ -83,9 +103,31 @@ class RoutedExperts(FeedForward):
         shared_gate = torch.empty((tokens,), dtype=torch.float32, device=device) if spec.shared_gate else None
         kernels.moe_route(hidden, self.router, self.correction, self.shared_gate, chosen, weights, shared_gate, spec.top,
                           spec.score == "softmax", spec.renormalize)
-        inner = torch.empty((tokens, spec.top, spec.intermediate), dtype=hidden.dtype, device=device)
-        kernels.moe_gate_up(hidden, self.gate_up, chosen, inner)
         shared_out = None if self.shared is None else self.shared.forward(hidden, step)
         out = torch.empty((tokens, spec.hidden), dtype=torch.float32, device=device)
+        if self.interleave and not step.all_single and tokens * spec.top >= GROUPED_FROM and not torch.cuda.is_current_stream_capturing():
+            self._grouped(hidden, chosen, weights, shared_out, shared_gate, out)
+            return out
+        inner = torch.empty((tokens, spec.top, spec.intermediate), dtype=hidden.dtype, device=device)
+        kernels.moe_gate_up(hidden, self.gate_up, chosen, inner, self.interleave)
         kernels.moe_down(inner, self.down, chosen, weights, shared_out, shared_gate, out)
         return out
+
+    def _grouped(self, hidden, chosen, weights, shared_out, shared_gate, out) -> None:
+        spec = self.spec
+        pairs, device = chosen.numel(), hidden.device
+        offsets = torch.empty(spec.experts + 1, dtype=torch.int32, device=device)
+        order = torch.empty(pairs, dtype=torch.int32, device=device)
+        position = torch.empty(pairs, dtype=torch.int32, device=device)
+        kernels.moe_sort(chosen, spec.experts, offsets, order, position)
+        bounds = offsets.tolist()                        # the host waits here for the router
+        gathered = torch.empty((pairs, spec.hidden), dtype=hidden.dtype, device=device)
+        kernels.moe_gather(hidden, order, spec.top, gathered)
+        inner = torch.empty((pairs, spec.intermediate), dtype=hidden.dtype, device=device)
+        rows = torch.empty((pairs, spec.hidden), dtype=torch.float32, device=device)
+        for expert in range(spec.experts):
+            begin, end = bounds[expert], bounds[expert + 1]
+            if end > begin:
+                kernels.linear_gated(gathered[begin:end], self.gate_up[expert], inner[begin:end])
+                kernels.linear(inner[begin:end], self.down[expert], None, rows[begin:end])
+        kernels.moe_combine(rows, position, weights, shared_out, shared_gate, out)

@@ -35,9 +35,12 @@ def run(arguments, lines=None, out=None) -> int:
     out = sys.stdout if out is None else out
     print(f"[trace_run] loading {arguments.model} ({arguments.dtype})", file=sys.stderr, flush=True)
     from .api import load_engine
+    from .cache import PAGE_TOKENS
     from .engine.batch import StepEntry
 
-    engine = load_engine(arguments.model, arguments.dtype, "gpu", max_tokens=arguments.max_tokens,
+    # `--max-tokens` counts the tokens that live requests hold; the cache hands out whole pages, so each request may need up to a
+    # page more than its tokens.  Room for 64 such roundings is added.
+    engine = load_engine(arguments.model, arguments.dtype, "gpu", max_tokens=arguments.max_tokens + 64 * PAGE_TOKENS,
                          enforce_declared_dtype=False)
     os.makedirs(arguments.out, exist_ok=True)
     slots: Dict[str, int] = {}
