@@ -1041,3 +1041,24 @@ TAU_EXPORT int tau_gemm_tc(int out_dtype, const void* x, const void* w, const fl
     if (out_dtype == TAU_BF16) return dispatch<bf16, false>(weight_map, input_map, box, bias, out, M, N, K, out_stride, plan, s);
     return dispatch<float, false>(weight_map, input_map, box, bias, out, M, N, K, out_stride, plan, s);
 }
+
+// One product per group of consecutive rows, each with a weight of its own: rows bounds[g] .. bounds[g + 1] of `x` (and of
+// `out`) meet the weight `w + g * w_group` (elements).  `bounds` is host memory, `groups + 1` ascending row numbers.  The
+// products are launched one after another from here, which costs a fraction of a launch through a foreign-function call each.
+TAU_EXPORT int tau_gemm_tc_groups(int out_dtype, const void* x, const void* w, void* out, const int* bounds, int groups, int N, int K,
+                                  long long x_stride, long long w_stride, long long out_stride, long long w_group, int gated, void* workspace,
+                                  long long workspace_floats, void* tickets, void* stream) {
+    if (!bounds || groups <= 0) return cudaErrorInvalidValue;
+    const size_t out_bytes = out_dtype == TAU_F32 ? 4 : 2;
+    for (int group = 0; group < groups; ++group) {
+        const int begin = bounds[group], rows = bounds[group + 1] - begin;
+        if (rows < 0) return cudaErrorInvalidValue;
+        if (rows == 0) continue;
+        const int status = tau_gemm_tc(out_dtype, static_cast<const bf16*>(x) + static_cast<size_t>(begin) * x_stride,
+                                       static_cast<const bf16*>(w) + static_cast<size_t>(group) * w_group, nullptr,
+                                       static_cast<char*>(out) + static_cast<size_t>(begin) * out_stride * out_bytes, rows, N, K, x_stride, w_stride,
+                                       out_stride, 0, gated, 0, workspace, workspace_floats, tickets, -1, 1, stream);
+        if (status != 0) return status;
+    }
+    return 0;
+}

@@ -83,7 +83,7 @@ _CLASS_OF = {
     "attention_decode": "attention", "attention_prefill": "attention", "attention_prefill_tc": "attention", "argmax": "selection",
     "sample_gumbel": "selection", "store_words_host": "selection", "random_normal": "other",
     "stream_add_norm": "norm", "gated_group_norm": "norm", "gemm_simt_batched": "product", "linear_recurrence": "recurrence",
-    "latent_prepare": "attention", "latent_attention": "attention", "moe_route": "routing", "moe_gate_up": "product", "moe_down": "product", "moe_sort": "routing", "moe_gather": "routing",
+    "latent_prepare": "attention", "latent_attention": "attention", "moe_route": "routing", "moe_gate_up": "experts", "moe_down": "experts", "gemm_tc_groups": "experts", "moe_sort": "routing", "moe_gather": "routing",
     "moe_combine": "routing",
 }
 _timing = None     # while timing: [last event, [(class, event after the launch), ...]]
@@ -391,6 +391,29 @@ def gemm_tc(values, weight, bias, out, token_box: int = 0, gated: bool = False, 
                                ctypes.c_longlong(weight.stride(0)), ctypes.c_longlong(out.stride(0)), ctypes.c_int(token_box),
                                ctypes.c_int(1 if gated else 0), ctypes.c_int(splits), _pointer(workspace),
                                ctypes.c_longlong(workspace.numel()), _pointer(tickets), ctypes.c_int(pair), ctypes.c_int(1 if cluster else 0), _stream()), "gemm_tc")
+
+
+def gemm_tc_groups(values, weights, out, bounds, gated: bool = False) -> None:
+    """One tensor-core product per group of consecutive rows: rows `bounds[g] .. bounds[g + 1]` of `values` [M, K] meet
+    `weights[g]` ([groups, N, K]) and land in the same rows of `out` ([M, N], or [M, N / 2] = silu(gate) * up with `gated`).
+    `bounds` is a host list of `groups + 1` ascending row numbers.  bfloat16, K % 8 == 0, 16-byte aligned rows."""
+    _on_device(values, weights, out)
+    rows, depth = values.shape
+    groups, features = weights.shape[0], weights.shape[1]
+    _require(weights.shape[2] == depth and weights.is_contiguous() and out.shape == (rows, features // 2 if gated else features),
+             "shapes must be [M,K] x [G,N,K] -> [M,N]")
+    _require(len(bounds) == groups + 1 and bounds[0] == 0 and bounds[-1] == rows, "bounds must run from 0 to the number of rows")
+    _require(values.dtype == weights.dtype == torch.bfloat16 and out.dtype in (torch.bfloat16, torch.float32) and (not gated or out.dtype == torch.bfloat16),
+             "inputs must be bfloat16 and the output bfloat16 or float32 (bfloat16 for a gated product)")
+    _require(_tc_fits(values, weights[0], out) and (not gated or features % 16 == 0), "needs K % 8 == 0 and 16-byte aligned rows")
+    library = build.load_library("gemm_tc.cu")
+    workspace, tickets = _tc_workspace_for(out.device)
+    table = (ctypes.c_int * (groups + 1))(*bounds)
+    launched = sum(1 for index in range(groups) if bounds[index + 1] > bounds[index])
+    _check(library.tau_gemm_tc_groups(_code(out), _pointer(values), _pointer(weights), _pointer(out), table, ctypes.c_int(groups), ctypes.c_int(features),
+                                      ctypes.c_int(depth), ctypes.c_longlong(values.stride(0)), ctypes.c_longlong(weights.stride(1)),
+                                      ctypes.c_longlong(out.stride(0)), ctypes.c_longlong(weights.stride(0)), ctypes.c_int(1 if gated else 0),
+                                      _pointer(workspace), ctypes.c_longlong(workspace.numel()), _pointer(tickets), _stream()), "gemm_tc_groups", launched)
 
 
 def gemm_tc_status() -> int:
@@ -721,12 +744,18 @@ def latent_prepare(down, latent_weight, eps: float, q, queries, rows, inv_freq, 
 LATENT_MAX_RANK = 512   # what the latent attention kernel keeps per lane
 
 
+_latent_scratch = {}
+_latent_scratch_kept = []
+
+
 def latent_attention(queries, rows, out, sinks, positions, token_seq, page_rows, n_heads: int, rank: int, rot_dim: int, scale: float,
-                     window: int = 0) -> None:
+                     window: int = 0, splits: int = 1) -> None:
     """Causal softmax attention of `queries` [tokens, n_heads, rank + rot_dim] over the cached rows [pages, 64, rank + rot_dim]
     of each token's sequence; a score is the dot product of a query with a row times `scale`; `out` [tokens, n_heads, rank]
     receives the weighted sums of the rows' first `rank` elements.  `sinks` (float32 [n_heads] or None): `exp(sink)` joins
-    the softmax denominator.  Scores, weights and sums are 32-bit."""
+    the softmax denominator.  Scores, weights and sums are 32-bit.  `splits` > 1 cuts every token's context into that many
+    ranges, one block each, whose results a second kernel joins (for steps of few tokens over long contexts); rows that are
+    not whole 16-byte vectors are served by a kernel that does not split."""
     _on_device(queries, rows, out, sinks, positions, token_seq, page_rows)
     tokens, width = queries.shape[0], rank + rot_dim
     _require(queries.shape == (tokens, n_heads, width) and queries.is_contiguous() and out.shape == (tokens, n_heads, rank) and out.is_contiguous()
@@ -737,11 +766,23 @@ def latent_attention(queries, rows, out, sinks, positions, token_seq, page_rows,
     _int_vector(positions, "positions")
     _int_vector(token_seq, "token_seq")
     _require(page_rows.dtype == torch.int32 and page_rows.dim() == 2 and page_rows.is_contiguous(), "page rows must be int32 [sequences, stride]")
+    _require(1 <= splits <= 64, "splits must lie between 1 and 64")
     library = build.load_library("latent_attention.cu")
+    library.tau_latent_attention_scratch.restype = ctypes.c_longlong
+    floats = library.tau_latent_attention_scratch(ctypes.c_int(tokens), ctypes.c_int(n_heads), ctypes.c_int(rank), ctypes.c_int(splits))
+    scratch = None
+    if floats:
+        key = (out.device, _stream_handle())
+        scratch = _latent_scratch.get(key)
+        if scratch is None or scratch.numel() < floats:
+            if scratch is not None:
+                _latent_scratch_kept.append(scratch)     # a captured graph may still name it
+            scratch = _latent_scratch[key] = torch.empty(max(floats, 1 << 20), dtype=torch.float32, device=out.device)
     _check(library.tau_latent_attention(
         _code(queries), _pointer(queries), _pointer(rows), _pointer(out), _pointer(sinks), _pointer(positions), _pointer(token_seq),
         _pointer(page_rows), ctypes.c_int(page_rows.shape[1]), ctypes.c_int(PAGE_TOKENS), ctypes.c_int(tokens), ctypes.c_int(n_heads),
-        ctypes.c_int(rank), ctypes.c_int(rot_dim), ctypes.c_float(scale), ctypes.c_int(window), _stream()), "latent_attention")
+        ctypes.c_int(rank), ctypes.c_int(rot_dim), ctypes.c_float(scale), ctypes.c_int(window), ctypes.c_int(splits), _pointer(scratch),
+        ctypes.c_longlong(0 if scratch is None else scratch.numel()), _stream()), "latent_attention", 2 if splits > 1 else 1)
 
 
 # ---------------------------------------------------------------------------- linear recurrences

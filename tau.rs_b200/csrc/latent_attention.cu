@@ -151,7 +151,187 @@ latent_attention_kernel(const T* __restrict__ queries, const T* __restrict__ row
     }
 }
 
+// The same attention with every cached row read once per head as 16-byte vectors and never staged: lane l of a head's warp
+// holds elements [8v, 8v + 8) (4 in 32-bit) of the query for v = l, l + 32, ..., reads the same elements of each row, and keeps
+// the weighted sums of exactly those elements, so the row that was read for the score is the row that is summed.  Two rows are
+// in flight at a time.  The context may be cut into `splits` ranges (grid.z): a range leaves (top, denominator, sums) in
+// `partial` and `latent_merge_kernel` joins them; with one range the warp finishes the head itself.
+template <typename T> struct RowVectors;
+template <> struct RowVectors<bf16> { static constexpr int n = 8, per_lane = 3; };
+template <> struct RowVectors<float> { static constexpr int n = 4, per_lane = 6; };
+constexpr int kVectorWidth = 768;      // 32 lanes x per_lane x n elements
+
+template <typename T> __device__ __forceinline__ void unpack_row(const uint4& raw, float (&out)[RowVectors<T>::n]);
+template <> __device__ __forceinline__ void unpack_row<bf16>(const uint4& raw, float (&out)[8]) {
+    const unsigned words[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        out[2 * i] = __uint_as_float(words[i] << 16);
+        out[2 * i + 1] = __uint_as_float(words[i] & 0xffff0000u);
+    }
+}
+template <> __device__ __forceinline__ void unpack_row<float>(const uint4& raw, float (&out)[4]) {
+    out[0] = __uint_as_float(raw.x); out[1] = __uint_as_float(raw.y); out[2] = __uint_as_float(raw.z); out[3] = __uint_as_float(raw.w);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kMaxWarps * 32)
+latent_attention_vec_kernel(const T* __restrict__ queries, const T* __restrict__ rows, T* __restrict__ out, const float* __restrict__ sinks,
+                            const int* __restrict__ positions, const int* __restrict__ token_seq, const int* __restrict__ page_rows, int page_stride,
+                            int page_tokens, int heads, int rank, int rot, float scale, int window, int splits, float* __restrict__ partial) {
+    grid_dependents_launch();
+    grid_dependency_wait();
+    constexpr int n = RowVectors<T>::n, kPer = RowVectors<T>::per_lane;
+    const int token = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, split = blockIdx.z;
+    const int head = blockIdx.y * kMaxWarps + warp;
+    if (head >= heads) return;                               // the warps of a block never meet
+    const int width = rank + rot, vectors = width / n;
+    const int position = positions[token];
+    const int* pages = page_rows + static_cast<size_t>(token_seq[token]) * page_stride;
+    const int first = window > 0 ? max(0, position - window + 1) : 0;
+    const int chunk = (position + 1 - first + splits - 1) / splits;
+    const int begin = first + split * chunk, end = min(position + 1, begin + chunk);
+    float q[kPer][n], sums[kPer][n];
+    const T* query = queries + (static_cast<size_t>(token) * heads + head) * width;
+#pragma unroll
+    for (int i = 0; i < kPer; ++i) {
+        const int v = lane + 32 * i;
+#pragma unroll
+        for (int j = 0; j < n; ++j) q[i][j] = sums[i][j] = 0.0f;
+        if (v < vectors) {
+            unpack_row<T>(*reinterpret_cast<const uint4*>(query + v * n), q[i]);
+#pragma unroll
+            for (int j = 0; j < n; ++j) q[i][j] *= scale;
+        }
+    }
+    float top = -INFINITY, denominator = 0.0f;
+    int key = begin;
+    while (key < end) {
+        const int page_index = key / page_tokens;
+        const int stop = min(end, (page_index + 1) * page_tokens);
+        const T* row = rows + (static_cast<size_t>(pages[page_index]) * page_tokens + (key - page_index * page_tokens)) * width;
+        for (; key < stop; key += 2, row += 2 * static_cast<size_t>(width)) {
+            const bool pair = key + 1 < stop;
+            float a[kPer][n], b[kPer][n];
+            float dot_a = 0.0f, dot_b = 0.0f;
+#pragma unroll
+            for (int i = 0; i < kPer; ++i) {
+                const int v = lane + 32 * i;
+                if (v < vectors) {
+                    unpack_row<T>(*reinterpret_cast<const uint4*>(row + v * n), a[i]);
+                    if (pair) unpack_row<T>(*reinterpret_cast<const uint4*>(row + width + v * n), b[i]);
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < kPer; ++i) {
+                if (lane + 32 * i < vectors) {
+#pragma unroll
+                    for (int j = 0; j < n; ++j) {
+                        dot_a = fmaf(q[i][j], a[i][j], dot_a);
+                        if (pair) dot_b = fmaf(q[i][j], b[i][j], dot_b);
+                    }
+                }
+            }
+#pragma unroll
+            for (int offset = 16; offset > 0; offset >>= 1) {
+                dot_a += __shfl_xor_sync(0xffffffffu, dot_a, offset);
+                dot_b += __shfl_xor_sync(0xffffffffu, dot_b, offset);
+            }
+            const float new_top = pair ? fmaxf(top, fmaxf(dot_a, dot_b)) : fmaxf(top, dot_a);
+            const float rescale = expf(top - new_top);      // 0 the first time
+            const float weight_a = expf(dot_a - new_top), weight_b = pair ? expf(dot_b - new_top) : 0.0f;
+            denominator = denominator * rescale + weight_a + weight_b;
+            top = new_top;
+#pragma unroll
+            for (int i = 0; i < kPer; ++i) {
+                if (lane + 32 * i < vectors) {
+#pragma unroll
+                    for (int j = 0; j < n; ++j) {
+                        float value = fmaf(sums[i][j], rescale, weight_a * a[i][j]);
+                        if (pair) value = fmaf(weight_b, b[i][j], value);
+                        sums[i][j] = value;
+                    }
+                }
+            }
+        }
+        key = stop;      // the step of two may have overshot by one
+    }
+    if (splits > 1) {
+        float* record = partial + ((static_cast<size_t>(token) * heads + head) * splits + split) * (rank + 2);
+        if (lane == 0) { record[0] = top; record[1] = denominator; }
+#pragma unroll
+        for (int i = 0; i < kPer; ++i)
+#pragma unroll
+            for (int j = 0; j < n; ++j) {
+                const int column = (lane + 32 * i) * n + j;
+                if (column < rank) record[2 + column] = sums[i][j];
+            }
+        return;
+    }
+    float rescale = 1.0f;
+    if (sinks) {
+        const float sink = sinks[head];
+        const float new_top = fmaxf(top, sink);
+        rescale = expf(top - new_top);
+        denominator = denominator * rescale + expf(sink - new_top);
+    }
+    const float inverse = rescale / denominator;
+#pragma unroll
+    for (int i = 0; i < kPer; ++i)
+#pragma unroll
+        for (int j = 0; j < n; ++j) {
+            const int column = (lane + 32 * i) * n + j;
+            if (column < rank) out[(static_cast<size_t>(token) * heads + head) * rank + column] = from_float<T>(sums[i][j] * inverse);
+        }
+}
+
+// One block per (token, head): joins the ranges of a context in their order.
+template <typename T>
+__global__ void latent_merge_kernel(const float* __restrict__ partial, const float* __restrict__ sinks, T* __restrict__ out, int heads, int rank, int splits) {
+    grid_dependents_launch();
+    grid_dependency_wait();
+    const size_t item = blockIdx.x;
+    const float* records = partial + item * splits * (rank + 2);
+    float top = -INFINITY;
+    for (int split = 0; split < splits; ++split) top = fmaxf(top, records[static_cast<size_t>(split) * (rank + 2)]);
+    const float sink = sinks ? sinks[item % heads] : -INFINITY;
+    const float all_top = fmaxf(top, sink);
+    float denominator = sinks ? expf(sink - all_top) : 0.0f;
+    for (int split = 0; split < splits; ++split) {
+        const float* record = records + static_cast<size_t>(split) * (rank + 2);
+        denominator += expf(record[0] - all_top) * record[1];
+    }
+    for (int column = threadIdx.x; column < rank; column += blockDim.x) {
+        float sum = 0.0f;
+        for (int split = 0; split < splits; ++split) {
+            const float* record = records + static_cast<size_t>(split) * (rank + 2);
+            sum = fmaf(expf(record[0] - all_top), record[2 + column], sum);
+        }
+        out[item * rank + column] = from_float<T>(sum / denominator);
+    }
+}
+
+template <typename T>
+int launch_vec(const void* queries, const void* rows, void* out, const float* sinks, const int* positions, const int* token_seq, const int* page_rows,
+               int page_stride, int page_tokens, int tokens, int heads, int rank, int rot, float scale, int window, int splits, float* partial, cudaStream_t s) {
+    const int warps = heads < kMaxWarps ? heads : kMaxWarps;
+    tau_launch(latent_attention_vec_kernel<T>, dim3(tokens, (heads + kMaxWarps - 1) / kMaxWarps, splits), dim3(warps * 32), 0, s, static_cast<const T*>(queries),
+               static_cast<const T*>(rows), static_cast<T*>(out), sinks, positions, token_seq, page_rows, page_stride, page_tokens, heads, rank, rot, scale,
+               window, splits, partial);
+    if (splits > 1) {
+        const int status = tau_launch_status();
+        if (status != 0) return status;
+        tau_launch(latent_merge_kernel<T>, dim3(tokens * heads), dim3(128), 0, s, static_cast<const float*>(partial), sinks, static_cast<T*>(out), heads, rank, splits);
+    }
+    return tau_launch_status();
+}
+
 }  // namespace
+
+// Floats of scratch that `splits` ranges need.
+TAU_EXPORT long long tau_latent_attention_scratch(int tokens, int heads, int rank, int splits) {
+    return splits > 1 ? static_cast<long long>(tokens) * heads * splits * (rank + 2) : 0;
+}
 
 TAU_EXPORT int tau_latent_prepare(int dtype, const void* down, long long down_stride, const float* latent_weight, float eps, const void* q,
                                   long long q_stride, void* queries, void* rows, const float* inv_freq, int rotary, const int* positions,
@@ -177,11 +357,19 @@ TAU_EXPORT int tau_latent_prepare(int dtype, const void* down, long long down_st
 
 TAU_EXPORT int tau_latent_attention(int dtype, const void* queries, const void* rows, void* out, const float* sinks, const int* positions,
                                     const int* token_seq, const int* page_rows, int page_stride, int page_tokens, int tokens, int heads, int rank,
-                                    int rot, float scale, int window, void* stream) {
+                                    int rot, float scale, int window, int splits, float* partial, long long partial_floats, void* stream) {
     if (tokens <= 0) return 0;
-    if (!queries || !rows || !out || !positions || !token_seq || !page_rows || heads <= 0 || rank <= 0 || rank > 32 * kMaxOwned || rot < 0)
+    if (!queries || !rows || !out || !positions || !token_seq || !page_rows || heads <= 0 || rank <= 0 || rank > 32 * kMaxOwned || rot < 0 || splits < 1)
         return cudaErrorInvalidValue;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // Rows that are whole 16-byte vectors take the kernel that reads them as such; others the one that stages tiles.
+    const int per_vector = dtype == TAU_BF16 ? 8 : 4;
+    if ((rank + rot) % per_vector == 0 && rank + rot <= kVectorWidth && (dtype == TAU_BF16 || dtype == TAU_F32)) {
+        if (splits > 1 && (!partial || partial_floats < tau_latent_attention_scratch(tokens, heads, rank, splits))) return cudaErrorInvalidValue;
+        if (dtype == TAU_BF16)
+            return launch_vec<bf16>(queries, rows, out, sinks, positions, token_seq, page_rows, page_stride, page_tokens, tokens, heads, rank, rot, scale, window, splits, partial, s);
+        return launch_vec<float>(queries, rows, out, sinks, positions, token_seq, page_rows, page_stride, page_tokens, tokens, heads, rank, rot, scale, window, splits, partial, s);
+    }
     const int warps = heads < kMaxWarps ? heads : kMaxWarps;
     const int width = rank + rot;
     const size_t bytes = (static_cast<size_t>(kTile) * (width + 1) + static_cast<size_t>(warps) * width) * sizeof(float);

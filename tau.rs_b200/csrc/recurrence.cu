@@ -22,7 +22,7 @@
 namespace {
 
 constexpr int kDim = TAU_KEY_DIM;
-constexpr int kSplit = kDim <= 64 ? 1 : kDim <= 128 ? 2 : kDim <= 256 ? 4 : 8;   // threads that share a column
+constexpr int kSplit = kDim <= 16 ? 1 : kDim <= 32 ? 2 : kDim <= 64 ? 4 : kDim <= 128 ? 8 : kDim <= 256 ? 16 : 32;   // threads that share a column
 constexpr int kRows = (kDim + kSplit - 1) / kSplit;                               // key rows per thread
 constexpr int kColumns = 32;                                                      // columns of a block (n included)
 
@@ -36,7 +36,7 @@ linear_recurrence_kernel(const T* __restrict__ q, const T* __restrict__ k, const
                          int heads, int value_dim, int exponential, float gate_cap, float query_scale, int activation) {
     grid_dependents_launch();
     grid_dependency_wait();
-    __shared__ float qs[kDim], ks[kDim], partial[kSplit][kColumns], scalars[4];
+    __shared__ float qs[2][kDim], ks[2][kDim], partial[kSplit][kColumns], scalars[2];
     const int head = blockIdx.x, sequence = blockIdx.y;
     const int columns = value_dim + (exponential ? 1 : 0);           // n rides as one more column of the state
     // A block serves a tile of value columns; with the exponential gating its last thread column serves n as well, in every
@@ -54,47 +54,83 @@ linear_recurrence_kernel(const T* __restrict__ q, const T* __restrict__ k, const
     float m = exponential ? record[static_cast<size_t>(columns) * kDim] : 0.0f;
     const float decay = exponential ? 1.0f : decays[head];
     const int begin = cu_seqlens[sequence], end = cu_seqlens[sequence + 1];
-    for (int token = begin; token < end; ++token) {
+    // The next token's q, k, v and gates are asked for before the current token is computed and put into the other half of
+    // qs/ks afterwards, so the walk along the sequence does not wait for memory at every token.
+    constexpr int kStage = (kDim + kColumns * kSplit - 1) / (kColumns * kSplit);
+    float next_q[kStage], next_k[kStage], next_v = 0.0f, next_in = 0.0f, next_forget = 0.0f;
+    auto fetch = [&](int token) {
         const size_t row = static_cast<size_t>(token) * stride;
-        for (int d = threadIdx.x; d < kDim; d += blockDim.x) {
-            qs[d] = activate(to_float(q[row + head * kDim + d]), activation) * query_scale;
-            ks[d] = activate(to_float(k[row + head * kDim + d]), activation);
+#pragma unroll
+        for (int i = 0; i < kStage; ++i) {
+            const int d = threadIdx.x + i * kColumns * kSplit;
+            if (d < kDim) {
+                next_q[i] = to_float(q[row + head * kDim + d]);
+                next_k[i] = to_float(k[row + head * kDim + d]);
+            }
         }
+        if (live && !is_n) next_v = to_float(v[row + head * value_dim + column]);
+        if (exponential) {
+            next_in = gates[static_cast<size_t>(token) * 2 * heads + head];
+            next_forget = gates[static_cast<size_t>(token) * 2 * heads + heads + head];
+        }
+    };
+    auto publish = [&](int half) {
+#pragma unroll
+        for (int i = 0; i < kStage; ++i) {
+            const int d = threadIdx.x + i * kColumns * kSplit;
+            if (d < kDim) {
+                qs[half][d] = activate(next_q[i], activation) * query_scale;
+                ks[half][d] = activate(next_k[i], activation);
+            }
+        }
+    };
+    if (begin < end) {
+        fetch(begin);
+        publish(0);
+    }
+    __syncthreads();
+    for (int token = begin; token < end; ++token) {
+        const int half = (token - begin) & 1;
+        const float raw_value = next_v, raw_in = next_in, raw_forget = next_forget;
+        if (token + 1 < end) fetch(token + 1);
         float keep = decay, take = 1.0f;
         if (exponential) {
-            const float log_in = gate_cap * tanhf(gates[static_cast<size_t>(token) * 2 * heads + head] / gate_cap);
-            const float capped = gate_cap * tanhf(gates[static_cast<size_t>(token) * 2 * heads + heads + head] / gate_cap);
+            const float log_in = gate_cap * tanhf(raw_in / gate_cap);
+            const float capped = gate_cap * tanhf(raw_forget / gate_cap);
             const float log_forget = fminf(capped, 0.0f) - log1pf(expf(-fabsf(capped)));     // logsigmoid
             const float m_new = fmaxf(log_forget + m, log_in);
             keep = expf(log_forget + m - m_new);
             take = expf(log_in - m_new);
             m = m_new;
         }
-        __syncthreads();
-        const float value = is_n ? 1.0f : live ? activate(to_float(v[row + head * value_dim + column]), activation) : 0.0f;
+        const float value = is_n ? 1.0f : live ? activate(raw_value, activation) : 0.0f;
         const float scaled = take * value;
-        float sum = 0.0f;
+        float sums[4] = {0.0f, 0.0f, 0.0f, 0.0f};      // four chains, so that a sum does not wait for the one before it
 #pragma unroll
         for (int r = 0; r < kRows; ++r) {
             if (row0 + r < kDim) {
-                S[r] = fmaf(keep, S[r], ks[row0 + r] * scaled);
-                sum = fmaf(S[r], qs[row0 + r], sum);
+                S[r] = fmaf(keep, S[r], ks[half][row0 + r] * scaled);
+                sums[r & 3] = fmaf(S[r], qs[half][row0 + r], sums[r & 3]);
             }
         }
+        float sum = (sums[0] + sums[1]) + (sums[2] + sums[3]);
         if (kSplit > 1) {
-            partial[part][threadIdx.x % kColumns] = sum;
+            partial[part][local] = sum;
             __syncthreads();
             sum = 0.0f;
 #pragma unroll
-            for (int p = 0; p < kSplit; ++p) sum += partial[p][threadIdx.x % kColumns];
+            for (int p = 0; p < kSplit; ++p) sum += partial[p][local];
         }
         if (exponential) {
-            if (is_n && part == 0) scalars[0] = fmaxf(fabsf(sum), expf(-m)) + 1e-6f;
+            if (is_n && part == 0) scalars[half] = fmaxf(fabsf(sum), expf(-m)) + 1e-6f;
+            if (token + 1 < end) publish(half ^ 1);
             __syncthreads();
-            sum /= scalars[0];
+            sum /= scalars[half];
+        } else {
+            if (token + 1 < end) publish(half ^ 1);
+            __syncthreads();
         }
         if (live && !is_n && part == 0) out[static_cast<size_t>(token) * heads * value_dim + head * value_dim + column] = sum;
-        __syncthreads();    // qs, ks, partial and scalars are written again for the next token
     }
     if (live && (!is_n || blockIdx.z == 0)) {
 #pragma unroll

@@ -58,6 +58,10 @@ class LatentAttention(Mixer):
     def cache_need(self):
         return CacheNeed("rows", row_width=self.row_width, window=self.spec.window)
 
+    def decode_blocks(self) -> int:
+        """Blocks per sequence and context range of a decode step: one for every eight heads."""
+        return -(-self.spec.n_heads // 8)
+
     def tensor_specs(self):
         specs = dict(self._own)
         for part in self._linears:
@@ -100,8 +104,13 @@ class LatentAttention(Mixer):
         kernels.gemm_simt_batched(q.view(tokens, spec.n_heads, spec.head_dim + spec.rot_dim)[:, :, : spec.head_dim], self.key_up_transposed,
                                   queries[:, :, : spec.kv_rank])
         summed = torch.empty((tokens, spec.n_heads, spec.kv_rank), dtype=hidden.dtype, device=hidden.device)
+        # A step of single tokens cuts each context into ranges so that the machine has blocks enough; the number is the engine's
+        # (part of a captured graph's key) or chosen here from the longest context.
+        splits = 1
+        if step.all_single:
+            splits = min(step.decode_splits or kernels.decode_splits(step.n_seqs, step.max_len, self.decode_blocks()), 64)
         kernels.latent_attention(queries, cache.rows, summed, self.sink, step.positions, step.token_seq, pages, spec.n_heads, spec.kv_rank,
-                                 spec.rot_dim, spec.softmax_scale, spec.window or 0)
+                                 spec.rot_dim, spec.softmax_scale, spec.window or 0, splits)
         if not spec.gate:
             mixed = torch.empty((tokens, self.v_width), dtype=hidden.dtype, device=hidden.device)
             kernels.gemm_simt_batched(summed, self.value_up, mixed.view(tokens, spec.n_heads, spec.value_dim))

@@ -52,7 +52,7 @@ class RoutedExperts(FeedForward):
             self._own[f"{prefix}.e{expert}.up"] = TensorSpec((spec.intermediate, spec.hidden), role="matrix")
             self._own[f"{prefix}.e{expert}.down"] = TensorSpec((spec.hidden, spec.intermediate), role="matrix")
         # Where the gated product exists the experts' gate and up rows are interleaved for it (as a dense feed-forward's are).
-        self.interleave = kernels.GATE_GROUP if kernels.gated_fits(spec.hidden, spec.intermediate, dtype) else 0
+        self.interleave = kernels.GATE_GROUP if kernels.gated_fits(spec.hidden, spec.intermediate, dtype) and spec.intermediate % 8 == 0 else 0
         self._held = {}
         self.router = self.correction = self.shared_gate = self.gate_up = self.down = None
 
@@ -125,9 +125,6 @@ class RoutedExperts(FeedForward):
         kernels.moe_gather(hidden, order, spec.top, gathered)
         inner = torch.empty((pairs, spec.intermediate), dtype=hidden.dtype, device=device)
         rows = torch.empty((pairs, spec.hidden), dtype=torch.float32, device=device)
-        for expert in range(spec.experts):
-            begin, end = bounds[expert], bounds[expert + 1]
-            if end > begin:
-                kernels.linear_gated(gathered[begin:end], self.gate_up[expert], inner[begin:end])
-                kernels.linear(inner[begin:end], self.down[expert], None, rows[begin:end])
+        kernels.gemm_tc_groups(gathered, self.gate_up, inner, bounds, gated=True)
+        kernels.gemm_tc_groups(inner, self.down, rows, bounds)
         kernels.moe_combine(rows, position, weights, shared_out, shared_gate, out)

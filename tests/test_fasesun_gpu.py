@@ -309,3 +309,32 @@ def test_trace_replay_of_a_fasesun_folder(models, tmp_path):
     rows = np.fromfile(out / "3.f32", dtype="<f4").reshape(2, cfg["vocab"])
     assert relative_error(torch.from_numpy(rows), torch.stack([wanted_a[68], wanted_b[32]])) < TOLERANCE["float32"]
     assert not (out / "4.f32").exists()
+
+
+def test_the_command_line_on_a_fasesun_folder(models, tmp_path):
+    """`bin/tau` on a Fasesun folder: greedy tokens in 32-bit equal those of `generate()`, with graphs and without, in chunks of
+    prompt tokens; bfloat16 runs from the same folder (the design stores bfloat16, so a folder need not say so); random
+    weights are written for a Fasesun config.json and read back."""
+    folder, cfg, values = models["mixed"]
+    prompts = [tokens_for(cfg, 40, 80), tokens_for(cfg, 7, 81)]
+    wanted = [list(result.tokens) for result in generate(folder, prompts, max_new_tokens=8, dtype="float32", stop_tokens=[])]
+
+    def run(arguments):
+        done = subprocess.run([os.path.join(ROOT, "bin", "tau")] + arguments, capture_output=True, text=True, timeout=900)
+        assert done.returncode == 0, done.stderr[-2000:]
+        return [json.loads(line) for line in done.stdout.splitlines() if line.startswith("{")]
+
+    base = ["--model", folder, "--max-tokens", "8", "--stop-ids", ""]
+    for prompt in prompts:
+        base += ["--prompt-ids", ",".join(str(token) for token in prompt)]
+    records = run(base + ["--dtype", "f32"])
+    assert [record["tokens"] for record in records if "tokens" in record] == wanted
+    records = run(base + ["--dtype", "f32", "--cuda-graph", "none", "--prefill-chunk-size", "16"])
+    assert [record["tokens"] for record in records if "tokens" in record] == wanted
+    records = run(base + ["--dtype", "bf16"])
+    assert all(len(record["tokens"]) == 8 for record in records if "tokens" in record)
+    config_path = tmp_path / "config.json"
+    config_path.write_text(json.dumps(fm.PEAKY))
+    drawn = str(tmp_path / "drawn")
+    records = run(["--random-weights", str(config_path), "--model", drawn, "--seed", "4", "--max-tokens", "5", "--stop-ids", "", "--prompt-ids", "1,2,3"])
+    assert [len(record["tokens"]) for record in records if "tokens" in record] == [5]
