@@ -70,7 +70,7 @@ __global__ void __launch_bounds__(kWarps * 32)
 attention_prefill_kernel(const bf16* __restrict__ queries, const bf16* __restrict__ keys, const bf16* __restrict__ values,
                          bf16* __restrict__ out, const int* __restrict__ cu_seqlens, const int* __restrict__ seq_start,
                          const int* __restrict__ page_rows, int page_stride, int page_tokens, int n_seqs, int n_heads, int n_kv_heads,
-                         int heads_per_block, int passes, float scale, int window) {
+                         int heads_per_block, int passes, float scale, int window, const float* __restrict__ sinks) {
     grid_dependents_launch();
     grid_dependency_wait();
     extern __shared__ __align__(128) uint8_t tiles[];
@@ -258,6 +258,11 @@ attention_prefill_kernel(const bf16* __restrict__ queries, const bf16* __restric
     sum_lo += __shfl_xor_sync(0xffffffffu, sum_lo, 2);
     sum_hi += __shfl_xor_sync(0xffffffffu, sum_hi, 1);
     sum_hi += __shfl_xor_sync(0xffffffffu, sum_hi, 2);
+    if (sinks) {   // a sink per head: exp(sink) joins the denominator with no key or value behind it (the maxima are in powers of two)
+        const float sink = sinks[head] * 1.4426950408889634f;
+        sum_lo += exp2f(sink - max_lo);
+        sum_hi += exp2f(sink - max_hi);
+    }
     const float inverse_lo = 1.0f / sum_lo, inverse_hi = 1.0f / sum_hi;
     bf16* out_base = out + (static_cast<size_t>(row0 + tile * kTile) * n_heads + head) * D;
     const size_t row_stride = static_cast<size_t>(n_heads) * D;
@@ -285,7 +290,7 @@ TAU_EXPORT int tau_attention_prefill_head_dim() { return D; }
 // `max_blocks`: an upper bound of sum over sequences of ceil(new tokens / (16 * tiles per block)), from the host.
 TAU_EXPORT int tau_attention_prefill(const void* queries, const void* keys, const void* values, void* out, const int* cu_seqlens,
                                      const int* seq_start, const int* page_rows, int page_stride, int page_tokens, int n_seqs,
-                                     int n_tokens, int n_heads, int n_kv_heads, float scale, int window, void* stream) {
+                                     int n_tokens, int n_heads, int n_kv_heads, float scale, int window, const float* sinks, void* stream) {
     if (n_tokens <= 0 || n_seqs <= 0) return 0;
     if (!queries || !keys || !values || !out || !cu_seqlens || !seq_start || !page_rows || n_heads <= 0 || n_kv_heads <= 0 ||
         n_heads % n_kv_heads != 0 || page_tokens <= 0 || window < 0)
@@ -305,6 +310,6 @@ TAU_EXPORT int tau_attention_prefill(const void* queries, const void* keys, cons
     }
     tau_launch(attention_prefill_kernel, dim3(grid), dim3(kWarps * 32), kSharedBytes, static_cast<cudaStream_t>(stream), 
         static_cast<const bf16*>(queries), static_cast<const bf16*>(keys), static_cast<const bf16*>(values), static_cast<bf16*>(out),
-        cu_seqlens, seq_start, page_rows, page_stride, page_tokens, n_seqs, n_heads, n_kv_heads, heads_per_block, passes, scale, window);
+        cu_seqlens, seq_start, page_rows, page_stride, page_tokens, n_seqs, n_heads, n_kv_heads, heads_per_block, passes, scale, window, sinks);
     return tau_launch_status();
 }

@@ -83,7 +83,7 @@ _CLASS_OF = {
     "attention_decode": "attention", "attention_prefill": "attention", "attention_prefill_tc": "attention", "argmax": "selection",
     "sample_gumbel": "selection", "store_words_host": "selection", "random_normal": "other",
     "stream_add_norm": "norm", "gated_group_norm": "norm", "gemm_simt_batched": "product", "linear_recurrence": "recurrence",
-    "latent_prepare": "attention", "latent_attention": "attention", "moe_route": "routing", "moe_gate_up": "experts", "moe_down": "experts", "gemm_tc_groups": "experts", "moe_sort": "routing", "moe_gather": "routing",
+    "latent_prepare": "attention", "latent_attention": "attention", "latent_expand": "attention", "moe_route": "routing", "moe_gate_up": "experts", "moe_down": "experts", "gemm_tc_groups": "experts", "moe_sort": "routing", "moe_gather": "routing",
     "moe_combine": "routing",
 }
 _timing = None     # while timing: [last event, [(class, event after the launch), ...]]
@@ -437,6 +437,10 @@ def prefer_optimized(enabled: bool) -> None:
     _prefer_optimized = bool(enabled)
 
 
+def optimized_preferred() -> bool:
+    return _prefer_optimized
+
+
 def gated_fits(in_features: int, out_features: int, dtype) -> bool:
     """Whether `linear_gated` serves a gate/up pair of these sizes (else: `linear`, then `silu_mul`)."""
     return _prefer_optimized and dtype == torch.bfloat16 and in_features % 8 == 0 and out_features % GATE_GROUP == 0
@@ -633,9 +637,11 @@ def attention_decode_fused(projected, keys, values, out, step, page_rows, write_
 
 
 def attention_prefill(queries, keys, values, out, cu_seqlens, seq_start, page_rows, n_heads: int, n_kv_heads: int, head_dim: int,
-                      scale: float, window: int) -> None:
-    """bfloat16 causal attention of runs of new tokens (`cu_seqlens` bounds them, `seq_start` positions were cached before)."""
-    _on_device(queries, keys, values, out, cu_seqlens, seq_start, page_rows)
+                      scale: float, window: int, sinks=None) -> None:
+    """bfloat16 causal attention of runs of new tokens (`cu_seqlens` bounds them, `seq_start` positions were cached before).
+    `sinks` (float32 [n_heads] or None): `exp(sink)` joins each head's softmax denominator."""
+    _on_device(queries, keys, values, out, cu_seqlens, seq_start, page_rows, sinks)
+    _f32_vector(sinks, n_heads, "the sinks")
     tokens = queries.shape[0]
     n_seqs = seq_start.numel()
     _require(queries.dtype == torch.bfloat16 == out.dtype == keys.dtype == values.dtype, "the tensor-core prefill kernel is bfloat16 only")
@@ -653,7 +659,7 @@ def attention_prefill(queries, keys, values, out, cu_seqlens, seq_start, page_ro
     _check(library.tau_attention_prefill(
         _pointer(queries), _pointer(keys), _pointer(values), _pointer(out), _pointer(cu_seqlens), _pointer(seq_start), _pointer(page_rows),
         ctypes.c_int(page_rows.shape[1]), ctypes.c_int(PAGE_TOKENS), ctypes.c_int(n_seqs), ctypes.c_int(tokens), ctypes.c_int(n_heads),
-        ctypes.c_int(n_kv_heads), ctypes.c_float(scale), ctypes.c_int(window), _stream()), "attention_prefill")
+        ctypes.c_int(n_kv_heads), ctypes.c_float(scale), ctypes.c_int(window), _pointer(sinks), _stream()), "attention_prefill")
 
 
 _prefill_schedule = {}   # (device, stream) -> the two counters by which the blocks of the tensor-core prefill kernel share out its tiles
@@ -712,16 +718,22 @@ def attention(queries, keys, values, out, step, page_rows, n_heads: int, n_kv_he
 
 # ---------------------------------------------------------------------------- latent attention
 def latent_prepare(down, latent_weight, eps: float, q, queries, rows, inv_freq, rotary_dim: int, positions, token_seq, page_rows,
-                   n_heads: int, head_dim: int, rot_dim: int, rank: int, write_rows: bool = True) -> None:
+                   n_heads: int, head_dim: int, rot_dim: int, rank: int, write_rows: bool = True, latent_out=None) -> None:
     """`down` [tokens, rank + rot_dim]: its first `rank` elements, RMS-normed with `latent_weight`, and its last `rot_dim`,
     rotated, go to the token's row of the cache pages `rows` [pages, 64, rank + rot_dim].  `q` [tokens, n_heads *
     (head_dim + rot_dim)]: each head's last `rot_dim` elements, rotated, go to `queries[token, head, rank:]`
     (`queries` [tokens, n_heads, rank + rot_dim]; its first `rank` elements per head are another kernel's to fill).
-    The rotation turns the pair (2i, 2i + 1), i < rotary_dim / 2, by `position * inv_freq[i]`."""
-    _on_device(down, latent_weight, q, queries, rows, inv_freq, positions, token_seq, page_rows)
+    The rotation turns the pair (2i, 2i + 1), i < rotary_dim / 2, by `position * inv_freq[i]`.  `queries` may be None (no query
+    is prepared); `latent_out` [tokens, rank] receives the normalised latents side by side as well."""
+    _on_device(down, latent_weight, q, queries, rows, inv_freq, positions, token_seq, page_rows, latent_out)
     tokens, width = q.shape[0], rank + rot_dim
-    _require(q.shape[1] == n_heads * (head_dim + rot_dim) and queries.shape == (tokens, n_heads, width) and queries.is_contiguous()
-             and queries.dtype == q.dtype, "queries must be [tokens, n_heads, rank + rot_dim]")
+    _require(q.shape[1] == n_heads * (head_dim + rot_dim), "q must be [tokens, n_heads * (head_dim + rot_dim)]")
+    if queries is not None:
+        _require(queries.shape == (tokens, n_heads, width) and queries.is_contiguous() and queries.dtype == q.dtype,
+                 "queries must be [tokens, n_heads, rank + rot_dim]")
+    if latent_out is not None:
+        _require(write_rows and latent_out.shape == (tokens, rank) and latent_out.is_contiguous() and latent_out.dtype == q.dtype,
+                 "the latents must be [tokens, rank]")
     _require(rotary_dim % 2 == 0 and 0 <= rotary_dim <= rot_dim, "rotary_dim must be even and at most rot_dim")
     if rotary_dim:
         _f32_vector(inv_freq, rotary_dim // 2, "the rotation's frequencies")
@@ -737,8 +749,50 @@ def latent_prepare(down, latent_weight, eps: float, q, queries, rows, inv_freq, 
         _code(q), _pointer(down), ctypes.c_longlong(down.stride(0) if write_rows else 0), _pointer(latent_weight), ctypes.c_float(eps), _pointer(q),
         ctypes.c_longlong(q.stride(0)), _pointer(queries), _pointer(rows), _pointer(inv_freq), ctypes.c_int(rotary_dim), _pointer(positions),
         _pointer(token_seq), _pointer(page_rows), ctypes.c_int(page_rows.shape[1]), ctypes.c_int(PAGE_TOKENS), ctypes.c_int(tokens),
-        ctypes.c_int(n_heads), ctypes.c_int(head_dim), ctypes.c_int(rot_dim), ctypes.c_int(rank), ctypes.c_int(1 if write_rows else 0), _stream()),
-        "latent_prepare")
+        ctypes.c_int(n_heads), ctypes.c_int(head_dim), ctypes.c_int(rot_dim), ctypes.c_int(rank), ctypes.c_int(1 if write_rows else 0),
+        _pointer(latent_out), _stream()), "latent_prepare")
+
+
+def latent_expand(q, down, expanded, queries, key_pages, value_pages, inv_freq, rotary_dim: int, positions, token_seq, pages_per_sequence: int,
+                  n_heads: int, head_dim: int, rot_dim: int, rank: int, value_dim: int) -> None:
+    """For runs that start at position 0: writes every head's query `[unrotated | rotated]` to `queries` [tokens, n_heads,
+    head_dim + rot_dim], its key `[expanded unrotated part | rotated shared part]` and its value `[expanded | zeros]` to pages
+    of their own ([sequences * pages_per_sequence, n_heads, 64, head_dim + rot_dim]; sequence `s` owns the pages from
+    `s * pages_per_sequence`).  `expanded` [tokens, n_heads * (head_dim + value_dim)] holds all heads' unrotated keys, then all
+    heads' values; `down` [tokens, rank + rot_dim] the shared key part behind the latent; `q` the projected queries."""
+    _on_device(q, down, expanded, queries, key_pages, value_pages, inv_freq, positions, token_seq)
+    tokens, width = q.shape[0], head_dim + rot_dim
+    _require(q.shape[1] == n_heads * width and down.shape == (tokens, rank + rot_dim) and expanded.shape == (tokens, n_heads * (head_dim + value_dim))
+             and expanded.is_contiguous(), "q, down and expanded must be [tokens, heads * (d + r)], [tokens, rank + r], [tokens, heads * (d + v)]")
+    _require(queries.shape == (tokens, n_heads, width) and queries.is_contiguous(), "queries must be [tokens, n_heads, head_dim + rot_dim]")
+    _require(key_pages.shape[1:] == (n_heads, PAGE_TOKENS, width) and key_pages.shape == value_pages.shape and key_pages.is_contiguous()
+             and value_pages.is_contiguous() and key_pages.shape[0] % pages_per_sequence == 0, "pages must be [sequences * pages, n_heads, 64, width]")
+    _require(q.dtype == down.dtype == expanded.dtype == queries.dtype == key_pages.dtype == value_pages.dtype, "one dtype throughout")
+    _require(value_dim <= width and rotary_dim % 2 == 0 and rotary_dim <= rot_dim, "values may not be wider than keys")
+    if rotary_dim:
+        _f32_vector(inv_freq, rotary_dim // 2, "the rotation's frequencies")
+    _int_vector(positions, "positions")
+    _int_vector(token_seq, "token_seq")
+    library = build.load_library("latent_attention.cu")
+    _check(library.tau_latent_expand(
+        _code(q), _pointer(q), ctypes.c_longlong(q.stride(0)), _pointer(down), ctypes.c_longlong(down.stride(0)), _pointer(expanded), _pointer(queries),
+        _pointer(key_pages), _pointer(value_pages), _pointer(inv_freq), ctypes.c_int(rotary_dim), _pointer(positions), _pointer(token_seq),
+        ctypes.c_int(pages_per_sequence), ctypes.c_int(PAGE_TOKENS), ctypes.c_int(tokens), ctypes.c_int(n_heads), ctypes.c_int(head_dim),
+        ctypes.c_int(rot_dim), ctypes.c_int(rank), ctypes.c_int(value_dim), _stream()), "latent_expand")
+
+
+def head_gate(values, gate, out, n_heads: int, width: int, value_dim: int) -> None:
+    """`out[token, head, :] = values[token, head, :value_dim] * sigmoid(gate[token, head, :])`: `values` [tokens, n_heads * width],
+    `gate` [tokens, n_heads * value_dim] (rows any distance apart) or None, `out` [tokens, n_heads * value_dim]."""
+    _on_device(values, gate, out)
+    tokens = values.shape[0]
+    _require(values.shape == (tokens, n_heads * width) and values.is_contiguous() and out.shape == (tokens, n_heads * value_dim) and out.is_contiguous()
+             and out.dtype == values.dtype and value_dim <= width, "values must be [tokens, heads * width] and the output [tokens, heads * value_dim]")
+    if gate is not None:
+        _require(gate.shape == out.shape and gate.dtype == out.dtype and gate.stride(1) == 1, "the gate must match the output")
+    library = build.load_library("latent_attention.cu")
+    _check(library.tau_head_gate(_code(values), _pointer(values), _pointer(gate), ctypes.c_longlong(0 if gate is None else gate.stride(0)), _pointer(out),
+                                 ctypes.c_int(tokens), ctypes.c_int(n_heads), ctypes.c_int(width), ctypes.c_int(value_dim), _stream()), "latent_expand")
 
 
 LATENT_MAX_RANK = 512   # what the latent attention kernel keeps per lane

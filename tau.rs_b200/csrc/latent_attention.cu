@@ -22,7 +22,8 @@ __global__ void __launch_bounds__(256)
 latent_prepare_kernel(const T* __restrict__ down, long long down_stride, const float* __restrict__ latent_weight, float eps,
                       const T* __restrict__ q, long long q_stride, T* __restrict__ queries, T* __restrict__ rows,
                       const float* __restrict__ inv_freq, int rotary, const int* __restrict__ positions, const int* __restrict__ token_seq,
-                      const int* __restrict__ page_rows, int page_stride, int page_tokens, int heads, int head_dim, int rot, int rank, int write_rows) {
+                      const int* __restrict__ page_rows, int page_stride, int page_tokens, int heads, int head_dim, int rot, int rank, int write_rows,
+                      T* __restrict__ latent_out) {
     grid_dependents_launch();
     grid_dependency_wait();
     __shared__ float scratch[33];
@@ -38,8 +39,11 @@ latent_prepare_kernel(const T* __restrict__ down, long long down_stride, const f
             squares += value * value;
         }
         const float inverse = 1.0f / sqrtf(block_sum(squares, scratch) / static_cast<float>(rank) + eps);
-        for (int column = threadIdx.x; column < rank; column += blockDim.x)
-            target[column] = from_float<T>(to_float(source[column]) * inverse * latent_weight[column]);
+        for (int column = threadIdx.x; column < rank; column += blockDim.x) {
+            const T latent = from_float<T>(to_float(source[column]) * inverse * latent_weight[column]);
+            target[column] = latent;
+            if (latent_out) latent_out[static_cast<size_t>(token) * rank + column] = latent;     // the same values side by side, for products
+        }
         for (int pair = threadIdx.x; pair < rot / 2 + (rot & 1); pair += blockDim.x) {
             const int first = 2 * pair;
             float u = to_float(source[rank + first]), w = first + 1 < rot ? to_float(source[rank + first + 1]) : 0.0f;
@@ -53,6 +57,7 @@ latent_prepare_kernel(const T* __restrict__ down, long long down_stride, const f
             if (first + 1 < rot) target[rank + first + 1] = from_float<T>(w);
         }
     }
+    if (!queries) return;
     const int pairs = rot / 2 + (rot & 1);
     for (int item = threadIdx.x; item < heads * pairs; item += blockDim.x) {
         const int head = item / pairs, first = 2 * (item % pairs);
@@ -311,6 +316,67 @@ __global__ void latent_merge_kernel(const float* __restrict__ partial, const flo
     }
 }
 
+// For prompts that start at position 0: every head's full key [expanded unrotated part | rotated shared part] and value
+// [expanded | zeros up to the key's width] go to pages of their own (sequence s owns pages s * pages_per_sequence ...), and
+// every head's query [unrotated | rotated] to rows side by side, so that the attention kernels of ordinary heads serve them.
+// `expanded` holds, per token, all heads' unrotated keys and then all heads' values.  One block per token.
+template <typename T>
+__global__ void __launch_bounds__(256)
+latent_expand_kernel(const T* __restrict__ q, long long q_stride, const T* __restrict__ down, long long down_stride, const T* __restrict__ expanded,
+                     T* __restrict__ queries, T* __restrict__ key_pages, T* __restrict__ value_pages, const float* __restrict__ inv_freq, int rotary,
+                     const int* __restrict__ positions, const int* __restrict__ token_seq, int pages_per_sequence, int page_tokens, int heads,
+                     int head_dim, int rot, int rank, int value_dim) {
+    grid_dependents_launch();
+    grid_dependency_wait();
+    const int token = blockIdx.x, position = positions[token];
+    const int width = head_dim + rot;
+    const size_t page = static_cast<size_t>(token_seq[token]) * pages_per_sequence + position / page_tokens;
+    const T* q_row = q + static_cast<size_t>(token) * q_stride;
+    const T* shared_key = down + static_cast<size_t>(token) * down_stride + rank;
+    const T* expanded_row = expanded + static_cast<size_t>(token) * heads * (head_dim + value_dim);
+    for (int item = threadIdx.x; item < heads * width; item += blockDim.x) {
+        const int head = item / width, column = item % width;
+        float query, key;
+        if (column < head_dim) {
+            query = to_float(q_row[head * width + column]);
+            key = to_float(expanded_row[head * head_dim + column]);
+        } else {
+            const int e = column - head_dim, first = e & ~1;
+            const T* q_rot = q_row + head * width + head_dim;
+            query = to_float(q_rot[e]);
+            key = to_float(shared_key[e]);
+            if (first + 1 < rotary) {
+                float sine, cosine;
+                sincosf(static_cast<float>(position) * inv_freq[first / 2], &sine, &cosine);
+                const float qu = to_float(q_rot[first]), qw = to_float(q_rot[first + 1]);
+                const float ku = to_float(shared_key[first]), kw = to_float(shared_key[first + 1]);
+                query = (e & 1) ? qw * cosine + qu * sine : qu * cosine - qw * sine;
+                key = (e & 1) ? kw * cosine + ku * sine : ku * cosine - kw * sine;
+            }
+        }
+        queries[(static_cast<size_t>(token) * heads + head) * width + column] = from_float<T>(query);
+        const size_t slot = ((page * heads + head) * page_tokens + position % page_tokens) * width + column;
+        key_pages[slot] = from_float<T>(key);
+        value_pages[slot] = column < value_dim ? expanded_row[heads * head_dim + head * value_dim + column] : from_float<T>(0.0f);
+    }
+}
+
+// out[token, head, :value_dim] = values[token, head, :value_dim] * sigmoid(gate[token, head, :]) where a head's values are the
+// first `value_dim` of `width` elements.
+template <typename T>
+__global__ void head_gate_kernel(const T* __restrict__ values, const T* __restrict__ gate, long long gate_stride, T* __restrict__ out, int heads,
+                                 int width, int value_dim) {
+    grid_dependents_launch();
+    grid_dependency_wait();
+    const size_t token = blockIdx.x;
+    for (int item = threadIdx.x; item < heads * value_dim; item += blockDim.x) {
+        const int head = item / value_dim, column = item % value_dim;
+        float value = to_float(values[(token * heads + head) * width + column]);
+        if (gate) value *= 1.0f / (1.0f + expf(-to_float(gate[token * gate_stride + item])));
+        out[token * heads * value_dim + item] = from_float<T>(value);
+    }
+}
+
 template <typename T>
 int launch_vec(const void* queries, const void* rows, void* out, const float* sinks, const int* positions, const int* token_seq, const int* page_rows,
                int page_stride, int page_tokens, int tokens, int heads, int rank, int rot, float scale, int window, int splits, float* partial, cudaStream_t s) {
@@ -336,20 +402,20 @@ TAU_EXPORT long long tau_latent_attention_scratch(int tokens, int heads, int ran
 TAU_EXPORT int tau_latent_prepare(int dtype, const void* down, long long down_stride, const float* latent_weight, float eps, const void* q,
                                   long long q_stride, void* queries, void* rows, const float* inv_freq, int rotary, const int* positions,
                                   const int* token_seq, const int* page_rows, int page_stride, int page_tokens, int tokens, int heads,
-                                  int head_dim, int rot, int rank, int write_rows, void* stream) {
+                                  int head_dim, int rot, int rank, int write_rows, void* latent_out, void* stream) {
     if (tokens <= 0) return 0;
-    if (!q || !queries || !positions || !token_seq || heads <= 0 || rank <= 0 || rot < 0 || (rotary > 0 && !inv_freq) || rotary > rot
+    if (!q || !positions || !token_seq || heads <= 0 || rank <= 0 || rot < 0 || (rotary > 0 && !inv_freq) || rotary > rot
         || (write_rows && (!down || !latent_weight || !rows || !page_rows)))
         return cudaErrorInvalidValue;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (dtype == TAU_F32)
         tau_launch(latent_prepare_kernel<float>, dim3(tokens), dim3(256), 0, s, static_cast<const float*>(down), down_stride, latent_weight, eps,
                    static_cast<const float*>(q), q_stride, static_cast<float*>(queries), static_cast<float*>(rows), inv_freq, rotary, positions,
-                   token_seq, page_rows, page_stride, page_tokens, heads, head_dim, rot, rank, write_rows);
+                   token_seq, page_rows, page_stride, page_tokens, heads, head_dim, rot, rank, write_rows, static_cast<float*>(latent_out));
     else if (dtype == TAU_BF16)
         tau_launch(latent_prepare_kernel<bf16>, dim3(tokens), dim3(256), 0, s, static_cast<const bf16*>(down), down_stride, latent_weight, eps,
                    static_cast<const bf16*>(q), q_stride, static_cast<bf16*>(queries), static_cast<bf16*>(rows), inv_freq, rotary, positions,
-                   token_seq, page_rows, page_stride, page_tokens, heads, head_dim, rot, rank, write_rows);
+                   token_seq, page_rows, page_stride, page_tokens, heads, head_dim, rot, rank, write_rows, static_cast<bf16*>(latent_out));
     else
         return cudaErrorInvalidValue;
     return tau_launch_status();
@@ -388,5 +454,42 @@ TAU_EXPORT int tau_latent_attention(int dtype, const void* queries, const void* 
     } else {
         return cudaErrorInvalidValue;
     }
+    return tau_launch_status();
+}
+
+TAU_EXPORT int tau_latent_expand(int dtype, const void* q, long long q_stride, const void* down, long long down_stride, const void* expanded, void* queries,
+                                 void* key_pages, void* value_pages, const float* inv_freq, int rotary, const int* positions, const int* token_seq,
+                                 int pages_per_sequence, int page_tokens, int tokens, int heads, int head_dim, int rot, int rank, int value_dim, void* stream) {
+    if (tokens <= 0) return 0;
+    if (!q || !down || !expanded || !queries || !key_pages || !value_pages || !positions || !token_seq || heads <= 0 || head_dim <= 0 || rot < 0
+        || value_dim <= 0 || value_dim > head_dim + rot || rotary > rot || (rotary > 0 && !inv_freq) || pages_per_sequence <= 0)
+        return cudaErrorInvalidValue;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (dtype == TAU_BF16)
+        tau_launch(latent_expand_kernel<bf16>, dim3(tokens), dim3(256), 0, s, static_cast<const bf16*>(q), q_stride, static_cast<const bf16*>(down), down_stride,
+                   static_cast<const bf16*>(expanded), static_cast<bf16*>(queries), static_cast<bf16*>(key_pages), static_cast<bf16*>(value_pages), inv_freq,
+                   rotary, positions, token_seq, pages_per_sequence, page_tokens, heads, head_dim, rot, rank, value_dim);
+    else if (dtype == TAU_F32)
+        tau_launch(latent_expand_kernel<float>, dim3(tokens), dim3(256), 0, s, static_cast<const float*>(q), q_stride, static_cast<const float*>(down), down_stride,
+                   static_cast<const float*>(expanded), static_cast<float*>(queries), static_cast<float*>(key_pages), static_cast<float*>(value_pages), inv_freq,
+                   rotary, positions, token_seq, pages_per_sequence, page_tokens, heads, head_dim, rot, rank, value_dim);
+    else
+        return cudaErrorInvalidValue;
+    return tau_launch_status();
+}
+
+TAU_EXPORT int tau_head_gate(int dtype, const void* values, const void* gate, long long gate_stride, void* out, int tokens, int heads, int width,
+                             int value_dim, void* stream) {
+    if (tokens <= 0) return 0;
+    if (!values || !out || heads <= 0 || value_dim <= 0 || value_dim > width) return cudaErrorInvalidValue;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (dtype == TAU_BF16)
+        tau_launch(head_gate_kernel<bf16>, dim3(tokens), dim3(256), 0, s, static_cast<const bf16*>(values), static_cast<const bf16*>(gate), gate_stride,
+                   static_cast<bf16*>(out), heads, width, value_dim);
+    else if (dtype == TAU_F32)
+        tau_launch(head_gate_kernel<float>, dim3(tokens), dim3(256), 0, s, static_cast<const float*>(values), static_cast<const float*>(gate), gate_stride,
+                   static_cast<float*>(out), heads, width, value_dim);
+    else
+        return cudaErrorInvalidValue;
     return tau_launch_status();
 }

@@ -76,6 +76,7 @@ class StepContext:
     max_len: int                 # longest sequence after the step
     all_single: bool             # every sequence brings exactly one token
     decode_splits: int = 0       # context splits of decode attention, fixed by a captured graph (0: chosen per step)
+    all_fresh: bool = False      # every sequence starts at position 0 in this step (nothing of it is cached yet)
 
 
 def fill_step(layout: StepLayout, out: np.ndarray, entries: Sequence[StepEntry], starts: Sequence[int], cache) -> None:

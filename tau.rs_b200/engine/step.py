@@ -174,7 +174,9 @@ class Engine:
             staged = np.zeros(layout.total, dtype=np.int32)
             fill_step(layout, staged, entries, starts, self.cache)
             buffer.copy_(torch.from_numpy(staged))
-        return step_views(layout, buffer, max_new, max_len, all(len(entry.tokens) == 1 for entry in entries))
+        context = step_views(layout, buffer, max_new, max_len, all(len(entry.tokens) == 1 for entry in entries))
+        context.all_fresh = all(start == 0 for start in starts)
+        return context
 
     def step(self, entries: Sequence[StepEntry], device_tokens: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
         """Runs the entries' tokens; returns 32-bit logits `[wanted places, vocab]` in the order of the

@@ -7,11 +7,14 @@ Per token, with `h` the block's normalised input:
     score(i, j) = (q_a,i . key_a,j) * scale for j <= i;   softmax whose denominator also holds exp(sink_a)
     out = W_o (concatenated heads * sigmoid(W_g h))
 
-Only `[c | rotate(r)]` is cached, one row per position (`CacheNeed("rows")`).  The expansion never happens: since
+Only `[c | rotate(r)]` is cached, one row per position (`CacheNeed("rows")`).  Steps over cached positions never expand it: since
 `q . (W_uk,a c) = (W_uk,a^T q) . c`, each head's unrotated query is carried into the latent's space by one small product per
 head, the attention kernel scores `[W_uk,a^T q | rotated q]` against the cached rows as they lie and sums the rows' latent
-parts, and one more product per head (`W_uv,a`) turns that sum into the head's values.  Prompts and single tokens take the
-same kernels.  Tensor names under the prefix: `dq`, `dq.norm`, `uq`, `dkv`, `dkv.norm`, `uk`, `uv`, `sink`, `g`, `o`.
+parts, and one more product per head (`W_uv,a`) turns that sum into the head's values.  Single tokens, portions of prompts
+and everything in float32 take this form.  A bfloat16 step whose sequences all start at position 0 (whole prompts, `EXPAND_FROM`
+tokens or more) takes the other: there the cache holds nothing yet, so keys and values of the step's own tokens are expanded
+once by one tensor-core product, laid into pages of their own, and the attention kernel of ordinary heads (with the sink in its
+denominator) serves them; the latent rows are cached all the same for the steps that follow.  Tensor names under the prefix: `dq`, `dq.norm`, `uq`, `dkv`, `dkv.norm`, `uk`, `uv`, `sink`, `g`, `o`.
 """
 from __future__ import annotations
 
@@ -22,6 +25,10 @@ from ..weights.tensor_spec import TensorSpec
 from .base import CacheNeed, Mixer
 from .linear import StackedLinear
 from .registry import build, register_mixer
+
+
+EXPAND_FROM = 128            # tokens of a step from which whole prompts take the expanded form
+EXPAND_LIMIT = 4 << 30       # bytes of expanded keys and values that a step may ask for
 
 
 @register_mixer("latent_attention")
@@ -88,6 +95,41 @@ class LatentAttention(Mixer):
         # [heads, kv_rank, head_dim]: the product `W_uk,a^T q` reads its weight as [out, in] like every other.
         self.key_up_transposed = self._held.pop(f"{prefix}.uk").view(spec.n_heads, spec.head_dim, spec.kv_rank).transpose(1, 2).contiguous()
         self.value_up = self._held.pop(f"{prefix}.uv").view(spec.n_heads, spec.value_dim, spec.kv_rank)
+        # For the expanded form: all heads' key rows, then all heads' value rows, as one weight.
+        width = spec.head_dim + spec.rot_dim
+        self.expands = (self.dtype == torch.bfloat16 and width % 16 == 0 and 16 <= width <= 256 and spec.value_dim <= width and spec.kv_rank % 8 == 0)
+        self.expand_weight = None
+        if self.expands:
+            self.expand_weight = torch.cat([self.key_up_transposed.transpose(1, 2).reshape(-1, spec.kv_rank), self.value_up.reshape(-1, spec.kv_rank)]).contiguous()
+        self._page_tables = {}
+
+    def _expanded(self, hidden, projected, q, step, cache):
+        """Whole prompts: keys and values of the step's tokens expanded once, attention by the kernel of ordinary heads."""
+        spec = self.spec
+        tokens, device, width = hidden.shape[0], hidden.device, spec.head_dim + spec.rot_dim
+        latents = torch.empty((tokens, spec.kv_rank), dtype=hidden.dtype, device=device)
+        position = self.position
+        frequencies, rotary = (None, 0) if position is None else (position.inv_freq, spec.position.rotary_dim)
+        kernels.latent_prepare(projected[:, : self.row_width], self.kv_norm, spec.eps, q, None, cache.rows, frequencies, rotary, step.positions,
+                               step.token_seq, step.page_rows[cache.group], spec.n_heads, spec.head_dim, spec.rot_dim, spec.kv_rank, True, latents)
+        expanded = torch.empty((tokens, self.expand_weight.shape[0]), dtype=hidden.dtype, device=device)
+        kernels.linear(latents, self.expand_weight, None, expanded)
+        pages = -(-step.max_new // kernels.PAGE_TOKENS)
+        key = (step.n_seqs, pages)
+        table = self._page_tables.get(key)
+        if table is None:
+            table = self._page_tables[key] = torch.arange(step.n_seqs * pages, dtype=torch.int32, device=device).view(step.n_seqs, pages)
+        shape = (step.n_seqs * pages, spec.n_heads, kernels.PAGE_TOKENS, width)
+        keys, values = torch.empty(shape, dtype=hidden.dtype, device=device), torch.empty(shape, dtype=hidden.dtype, device=device)
+        queries = torch.empty((tokens, spec.n_heads, width), dtype=hidden.dtype, device=device)
+        kernels.latent_expand(q, projected[:, : self.row_width], expanded, queries, keys, values, frequencies, rotary, step.positions, step.token_seq,
+                              pages, spec.n_heads, spec.head_dim, spec.rot_dim, spec.kv_rank, spec.value_dim)
+        attended = torch.empty((tokens, spec.n_heads * width), dtype=hidden.dtype, device=device)
+        kernels.attention_prefill(queries.view(tokens, -1), keys, values, attended, step.cu_seqlens, step.seq_start, table, spec.n_heads, spec.n_heads,
+                                  width, spec.softmax_scale, spec.window or 0, self.sink)
+        gated = torch.empty((tokens, self.v_width), dtype=hidden.dtype, device=device)
+        kernels.head_gate(attended, projected[:, self.row_width :] if spec.gate else None, gated, spec.n_heads, width, spec.value_dim)
+        return self.out.forward(gated)
 
     def forward(self, hidden, step, cache, writes_cache: bool):
         spec = self.spec
@@ -96,6 +138,11 @@ class LatentAttention(Mixer):
         q_latent = torch.empty((tokens, spec.q_rank), dtype=hidden.dtype, device=hidden.device)
         kernels.rms_norm(self.down_q.forward(hidden), self.q_norm, spec.eps, q_latent)
         q = self.up_q.forward(q_latent)
+        if (self.expands and writes_cache and getattr(step, "all_fresh", False) and not step.all_single and tokens >= EXPAND_FROM
+                and kernels.optimized_preferred()):
+            pages = step.n_seqs * -(-step.max_new // kernels.PAGE_TOKENS)
+            if 4 * pages * spec.n_heads * kernels.PAGE_TOKENS * (spec.head_dim + spec.rot_dim) <= EXPAND_LIMIT:
+                return self._expanded(hidden, projected, q, step, cache)
         queries = torch.empty((tokens, spec.n_heads, self.row_width), dtype=hidden.dtype, device=hidden.device)
         pages = step.page_rows[cache.group]
         kernels.latent_prepare(projected[:, : self.row_width], self.kv_norm, spec.eps, q, queries, cache.rows,

@@ -60,9 +60,10 @@ def engine_of(models, name, dtype, max_tokens=1024):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("layer", [
     fm.latent(mlp=None), fm.latent(heads=1, dim=8, rot_dim=24, rot_dims=12, vdim=8, q_rank=16, kv_rank=16, scale=0.9, mlp=None),
+    fm.latent(heads=3, dim=32, rot_dim=16, rot_dims=16, vdim=40, q_rank=24, kv_rank=56, mlp=None),
     fm.mlstm(mlp=None), fm.mlstm(heads=3, dim=8, vdim=130, gate_cap=2.0, mlp=None),
     fm.lightning(mlp=None), fm.lightning(heads=2, dim=100, vdim=12, decay=[0.3, 1.0], mlp=None),
-], ids=["latent", "latent_one_head", "mlstm", "mlstm_wide_values", "lightning", "lightning_wide_keys"])
+], ids=["latent", "latent_one_head", "latent_expanding", "mlstm", "mlstm_wide_values", "lightning", "lightning_wide_keys"])
 def test_a_mixer_alone(tmp_path, layer, dtype):
     cfg = fm.config([layer], width=80, vocab=61)
     values = fm.write_model(str(tmp_path), cfg, 5)
@@ -239,7 +240,7 @@ def test_a_sharp_softmax_loses_no_key_far_away_or_at_a_page_border(models, dtype
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["mixed", "odd"])
+@pytest.mark.parametrize("name", ["mixed", "odd", "peaky"])
 def test_unequal_batches_against_each_request_alone(models, name, dtype):
     engine, cfg, values = engine_of(models, name, dtype, 2048)
     lengths, prompts = [90, 31, 140, 5, 66], [70, 1, 129, 3, 64]
