@@ -43,6 +43,53 @@ __device__ __forceinline__ float warp_dot<bf16>(const bf16* __restrict__ weights
     return warp_sum(sum);
 }
 
+// Two dot products at once (a gate row and its up row, or the rows of two places), so that a lane has four 16-byte loads in
+// flight where the rows allow them.
+template <typename T>
+__device__ __forceinline__ void warp_dot_pair(const T* __restrict__ first, const float* __restrict__ first_vector, const T* __restrict__ second,
+                                              const float* __restrict__ second_vector, int length, int lane, float& first_sum, float& second_sum) {
+    first_sum = warp_dot(first, first_vector, length, lane);
+    second_sum = warp_dot(second, second_vector, length, lane);
+}
+
+__device__ __forceinline__ float dot8(const uint4& raw, const float* __restrict__ vector) {
+    const unsigned words[4] = {raw.x, raw.y, raw.z, raw.w};
+    float sum = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        sum = fmaf(__uint_as_float(words[i] << 16), vector[2 * i], sum);
+        sum = fmaf(__uint_as_float(words[i] & 0xffff0000u), vector[2 * i + 1], sum);
+    }
+    return sum;
+}
+
+template <>
+__device__ __forceinline__ void warp_dot_pair<bf16>(const bf16* __restrict__ first, const float* __restrict__ first_vector, const bf16* __restrict__ second,
+                                                    const float* __restrict__ second_vector, int length, int lane, float& first_sum, float& second_sum) {
+    if (((reinterpret_cast<uintptr_t>(first) | reinterpret_cast<uintptr_t>(second)) & 15) != 0 || length % 8 != 0) {
+        first_sum = warp_dot(first, first_vector, length, lane);
+        second_sum = warp_dot(second, second_vector, length, lane);
+        return;
+    }
+    float a = 0.0f, b = 0.0f, c = 0.0f, d = 0.0f;
+    int column = lane * 8;
+    for (; column + 256 < length; column += 512) {
+        const uint4 a0 = *reinterpret_cast<const uint4*>(first + column), b0 = *reinterpret_cast<const uint4*>(second + column);
+        const uint4 a1 = *reinterpret_cast<const uint4*>(first + column + 256), b1 = *reinterpret_cast<const uint4*>(second + column + 256);
+        a += dot8(a0, first_vector + column);
+        b += dot8(b0, second_vector + column);
+        c += dot8(a1, first_vector + column + 256);
+        d += dot8(b1, second_vector + column + 256);
+    }
+    if (column < length) {
+        const uint4 a0 = *reinterpret_cast<const uint4*>(first + column), b0 = *reinterpret_cast<const uint4*>(second + column);
+        a += dot8(a0, first_vector + column);
+        b += dot8(b0, second_vector + column);
+    }
+    first_sum = warp_sum(a + c);
+    second_sum = warp_sum(b + d);
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kThreads)
 moe_route_kernel(const T* __restrict__ hidden, const float* __restrict__ router, const float* __restrict__ correction,
@@ -124,8 +171,8 @@ moe_gate_up_kernel(const T* __restrict__ hidden, const T* __restrict__ gate_up, 
         // Plain: gate rows, then up rows.  Interleaved: groups of `interleave` gate rows, each followed by its up rows.
         const int gate_row = interleave ? feature / interleave * 2 * interleave + feature % interleave : feature;
         const int up_row = interleave ? gate_row + interleave : inner + feature;
-        const float gate = warp_dot(weights + static_cast<size_t>(gate_row) * width, row, width, lane);
-        const float up = warp_dot(weights + static_cast<size_t>(up_row) * width, row, width, lane);
+        float gate, up;
+        warp_dot_pair(weights + static_cast<size_t>(gate_row) * width, row, weights + static_cast<size_t>(up_row) * width, row, width, lane, gate, up);
         if (lane == 0) inner_out[static_cast<size_t>(pair) * inner + feature] = from_float<T>(gate / (1.0f + expf(-gate)) * up);
     }
 }
@@ -145,7 +192,16 @@ moe_down_kernel(const T* __restrict__ inner_in, const T* __restrict__ down, cons
     const int begin = blockIdx.y * features_per_block, end = min(width, begin + features_per_block);
     for (int feature = begin + warp; feature < end; feature += kWarps) {
         float sum = 0.0f;
-        for (int place = 0; place < top; ++place) {
+        int place = 0;
+        for (; place + 1 < top; place += 2) {     // two places at a time, summed in place order
+            const T* first = down + (static_cast<size_t>(chosen[static_cast<size_t>(token) * top + place]) * width + feature) * inner;
+            const T* second = down + (static_cast<size_t>(chosen[static_cast<size_t>(token) * top + place + 1]) * width + feature) * inner;
+            float a, b;
+            warp_dot_pair(first, rows + place * inner, second, rows + (place + 1) * inner, inner, lane, a, b);
+            sum = fmaf(weights[static_cast<size_t>(token) * top + place], a, sum);
+            sum = fmaf(weights[static_cast<size_t>(token) * top + place + 1], b, sum);
+        }
+        if (place < top) {
             const T* weight_row = down + (static_cast<size_t>(chosen[static_cast<size_t>(token) * top + place]) * width + feature) * inner;
             sum = fmaf(weights[static_cast<size_t>(token) * top + place], warp_dot(weight_row, rows + place * inner, inner, lane), sum);
         }
