@@ -356,6 +356,15 @@ def design_comparison(args) -> int:
             decode_once()
             decode_classes = kernels.take_timing(stop=True)
             read = engine.bytes_read_by_a_decode_step()
+            if label == "fasesun":
+                # `bytes_read_by_a_decode_step` counts the experts that one token chooses; a batch whose tokens choose independently
+                # reads E (1 - (1 - top / E)^batch) of a layer's E experts on average.
+                for layer in config["layers"]:
+                    mlp = layer.get("mlp")
+                    if mlp:
+                        experts, top = mlp["router"]["experts"], mlp["router"]["top"]
+                        distinct = experts * (1.0 - (1.0 - top / experts) ** batch)
+                        read += int((distinct - top) * 3 * mlp["expert"]["ff"] * config["width"] * 2)
             record[label] = {
                 "prefill_tok_s": round(context / prefill_ms * 1e3, 1), "prefill_ms": round(prefill_ms, 3),
                 "decode_tok_s": round(batch / decode_ms * 1e3, 1), "decode_ms_per_step": round(decode_ms, 4),

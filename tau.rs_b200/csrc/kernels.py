@@ -850,7 +850,8 @@ def linear_recurrence(q, k, v, gates, decays, state, cu_seqlens, seq_slot, out, 
     `q`, `k` [tokens, n_heads * key_dim] and `v` [tokens, n_heads * value_dim] may be column ranges of one wider tensor (same
     row stride).  `state` [slots, floats per slot] is 32-bit and updated in place: per head `value_dim` columns of `key_dim`
     numbers, and with `exponential` one more column (the normaliser) and the running maximum.  `gates` [tokens, 2 * n_heads]
-    float32 are the pre-activations of the input gates, then of the forget gates; `decays` [n_heads] float32 otherwise.
+    float32 are the pre-activations of the input gates, then of the forget gates (overwritten with the log gates);
+    `decays` [n_heads] float32 otherwise.
     `out` [tokens, n_heads * value_dim] float32."""
     _on_device(q, k, v, gates, decays, state, cu_seqlens, seq_slot, out)
     tokens = q.shape[0]
@@ -874,9 +875,9 @@ def linear_recurrence(q, k, v, gates, decays, state, cu_seqlens, seq_slot, out, 
     library = build.load_library("recurrence.cu", (f"TAU_KEY_DIM={key_dim}",))
     _check(library.tau_linear_recurrence(
         _code(q), _pointer(q), _pointer(k), _pointer(v), ctypes.c_longlong(q.stride(0)), _pointer(gates), _pointer(decays), _pointer(state),
-        ctypes.c_longlong(state.stride(0)), _pointer(cu_seqlens), _pointer(seq_slot), _pointer(out), ctypes.c_int(n_seqs), ctypes.c_int(n_heads),
+        ctypes.c_longlong(state.stride(0)), _pointer(cu_seqlens), _pointer(seq_slot), _pointer(out), ctypes.c_int(tokens), ctypes.c_int(n_seqs), ctypes.c_int(n_heads),
         ctypes.c_int(value_dim), ctypes.c_int(1 if exponential else 0), ctypes.c_float(gate_cap), ctypes.c_float(query_scale),
-        ctypes.c_int(1 if silu else 0), _stream()), "linear_recurrence")
+        ctypes.c_int(1 if silu else 0), _stream()), "linear_recurrence", 2 if exponential else 1)
 
 
 # ---------------------------------------------------------------------------- routed experts

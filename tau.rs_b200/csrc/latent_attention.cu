@@ -179,8 +179,26 @@ template <> __device__ __forceinline__ void unpack_row<float>(const uint4& raw, 
     out[0] = __uint_as_float(raw.x); out[1] = __uint_as_float(raw.y); out[2] = __uint_as_float(raw.z); out[3] = __uint_as_float(raw.w);
 }
 
+// dot += q . a and sums += weight * a for one 16-byte vector of a row, unpacked on the way (rows and queries stay packed in
+// registers, which keeps two blocks of eight warps on an SM).
+template <typename T> __device__ __forceinline__ float vector_dot(const uint4& q, const uint4& a);
+template <> __device__ __forceinline__ float vector_dot<bf16>(const uint4& q, const uint4& a) {
+    const unsigned qw[4] = {q.x, q.y, q.z, q.w}, aw[4] = {a.x, a.y, a.z, a.w};
+    float dot = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        dot = fmaf(__uint_as_float(qw[i] << 16), __uint_as_float(aw[i] << 16), dot);
+        dot = fmaf(__uint_as_float(qw[i] & 0xffff0000u), __uint_as_float(aw[i] & 0xffff0000u), dot);
+    }
+    return dot;
+}
+template <> __device__ __forceinline__ float vector_dot<float>(const uint4& q, const uint4& a) {
+    return fmaf(__uint_as_float(q.x), __uint_as_float(a.x), fmaf(__uint_as_float(q.y), __uint_as_float(a.y),
+           fmaf(__uint_as_float(q.z), __uint_as_float(a.z), __uint_as_float(q.w) * __uint_as_float(a.w))));
+}
+
 template <typename T>
-__global__ void __launch_bounds__(kMaxWarps * 32)
+__global__ void __launch_bounds__(kMaxWarps * 32, 2)
 latent_attention_vec_kernel(const T* __restrict__ queries, const T* __restrict__ rows, T* __restrict__ out, const float* __restrict__ sinks,
                             const int* __restrict__ positions, const int* __restrict__ token_seq, const int* __restrict__ page_rows, int page_stride,
                             int page_tokens, int heads, int rank, int rot, float scale, int window, int splits, float* __restrict__ partial) {
@@ -196,18 +214,16 @@ latent_attention_vec_kernel(const T* __restrict__ queries, const T* __restrict__
     const int first = window > 0 ? max(0, position - window + 1) : 0;
     const int chunk = (position + 1 - first + splits - 1) / splits;
     const int begin = first + split * chunk, end = min(position + 1, begin + chunk);
-    float q[kPer][n], sums[kPer][n];
+    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+    uint4 q[kPer];
+    float sums[kPer][n];
     const T* query = queries + (static_cast<size_t>(token) * heads + head) * width;
 #pragma unroll
     for (int i = 0; i < kPer; ++i) {
         const int v = lane + 32 * i;
 #pragma unroll
-        for (int j = 0; j < n; ++j) q[i][j] = sums[i][j] = 0.0f;
-        if (v < vectors) {
-            unpack_row<T>(*reinterpret_cast<const uint4*>(query + v * n), q[i]);
-#pragma unroll
-            for (int j = 0; j < n; ++j) q[i][j] *= scale;
-        }
+        for (int j = 0; j < n; ++j) sums[i][j] = 0.0f;
+        q[i] = v < vectors ? *reinterpret_cast<const uint4*>(query + v * n) : zero;
     }
     float top = -INFINITY, denominator = 0.0f;
     int key = begin;
@@ -217,31 +233,26 @@ latent_attention_vec_kernel(const T* __restrict__ queries, const T* __restrict__
         const T* row = rows + (static_cast<size_t>(pages[page_index]) * page_tokens + (key - page_index * page_tokens)) * width;
         for (; key < stop; key += 2, row += 2 * static_cast<size_t>(width)) {
             const bool pair = key + 1 < stop;
-            float a[kPer][n], b[kPer][n];
-            float dot_a = 0.0f, dot_b = 0.0f;
+            uint4 a[kPer], b[kPer];
 #pragma unroll
             for (int i = 0; i < kPer; ++i) {
                 const int v = lane + 32 * i;
-                if (v < vectors) {
-                    unpack_row<T>(*reinterpret_cast<const uint4*>(row + v * n), a[i]);
-                    if (pair) unpack_row<T>(*reinterpret_cast<const uint4*>(row + width + v * n), b[i]);
-                }
+                a[i] = v < vectors ? *reinterpret_cast<const uint4*>(row + v * n) : zero;
+                b[i] = (pair && v < vectors) ? *reinterpret_cast<const uint4*>(row + width + v * n) : zero;
             }
+            float dot_a = 0.0f, dot_b = 0.0f;
 #pragma unroll
             for (int i = 0; i < kPer; ++i) {
-                if (lane + 32 * i < vectors) {
-#pragma unroll
-                    for (int j = 0; j < n; ++j) {
-                        dot_a = fmaf(q[i][j], a[i][j], dot_a);
-                        if (pair) dot_b = fmaf(q[i][j], b[i][j], dot_b);
-                    }
-                }
+                dot_a += vector_dot<T>(q[i], a[i]);
+                dot_b += vector_dot<T>(q[i], b[i]);
             }
 #pragma unroll
             for (int offset = 16; offset > 0; offset >>= 1) {
                 dot_a += __shfl_xor_sync(0xffffffffu, dot_a, offset);
                 dot_b += __shfl_xor_sync(0xffffffffu, dot_b, offset);
             }
+            dot_a *= scale;
+            dot_b *= scale;
             const float new_top = pair ? fmaxf(top, fmaxf(dot_a, dot_b)) : fmaxf(top, dot_a);
             const float rescale = expf(top - new_top);      // 0 the first time
             const float weight_a = expf(dot_a - new_top), weight_b = pair ? expf(dot_b - new_top) : 0.0f;
@@ -249,14 +260,11 @@ latent_attention_vec_kernel(const T* __restrict__ queries, const T* __restrict__
             top = new_top;
 #pragma unroll
             for (int i = 0; i < kPer; ++i) {
-                if (lane + 32 * i < vectors) {
+                float x[n], y[n];
+                unpack_row<T>(a[i], x);
+                unpack_row<T>(b[i], y);
 #pragma unroll
-                    for (int j = 0; j < n; ++j) {
-                        float value = fmaf(sums[i][j], rescale, weight_a * a[i][j]);
-                        if (pair) value = fmaf(weight_b, b[i][j], value);
-                        sums[i][j] = value;
-                    }
-                }
+                for (int j = 0; j < n; ++j) sums[i][j] = fmaf(weight_b, y[j], fmaf(sums[i][j], rescale, weight_a * x[j]));
             }
         }
         key = stop;      // the step of two may have overshot by one

@@ -23,20 +23,51 @@ __device__ __forceinline__ float warp_dot(const T* __restrict__ weights, const f
     return warp_sum(sum);
 }
 
+// 32-bit rows (the router's) that start on a 16-byte boundary are read four elements at a time.
+template <>
+__device__ __forceinline__ float warp_dot<float>(const float* __restrict__ weights, const float* __restrict__ vector, int length, int lane) {
+    float sum = 0.0f;
+    if ((reinterpret_cast<uintptr_t>(weights) & 15) == 0 && length % 4 == 0) {
+        float other = 0.0f;
+        int column = lane * 4;
+        for (; column + 128 < length; column += 256) {
+            const float4 w0 = *reinterpret_cast<const float4*>(weights + column), w1 = *reinterpret_cast<const float4*>(weights + column + 128);
+            const float4 x0 = *reinterpret_cast<const float4*>(vector + column), x1 = *reinterpret_cast<const float4*>(vector + column + 128);
+            sum = fmaf(w0.x, x0.x, fmaf(w0.y, x0.y, fmaf(w0.z, x0.z, fmaf(w0.w, x0.w, sum))));
+            other = fmaf(w1.x, x1.x, fmaf(w1.y, x1.y, fmaf(w1.z, x1.z, fmaf(w1.w, x1.w, other))));
+        }
+        if (column < length) {
+            const float4 w0 = *reinterpret_cast<const float4*>(weights + column), x0 = *reinterpret_cast<const float4*>(vector + column);
+            sum = fmaf(w0.x, x0.x, fmaf(w0.y, x0.y, fmaf(w0.z, x0.z, fmaf(w0.w, x0.w, sum))));
+        }
+        sum += other;
+    } else {
+        for (int column = lane; column < length; column += 32) sum = fmaf(weights[column], vector[column], sum);
+    }
+    return warp_sum(sum);
+}
+
+// Eight bfloat16 weights against eight floats of shared memory, which are read as two 16-byte words (lanes 32 bytes apart meet
+// two to a bank that way, not eight).
+__device__ __forceinline__ float dot8(const uint4& raw, const float* __restrict__ vector) {
+    const float4 low = *reinterpret_cast<const float4*>(vector), high = *reinterpret_cast<const float4*>(vector + 4);
+    float sum = __uint_as_float(raw.x << 16) * low.x;
+    sum = fmaf(__uint_as_float(raw.x & 0xffff0000u), low.y, sum);
+    sum = fmaf(__uint_as_float(raw.y << 16), low.z, sum);
+    sum = fmaf(__uint_as_float(raw.y & 0xffff0000u), low.w, sum);
+    sum = fmaf(__uint_as_float(raw.z << 16), high.x, sum);
+    sum = fmaf(__uint_as_float(raw.z & 0xffff0000u), high.y, sum);
+    sum = fmaf(__uint_as_float(raw.w << 16), high.z, sum);
+    sum = fmaf(__uint_as_float(raw.w & 0xffff0000u), high.w, sum);
+    return sum;
+}
+
 // bfloat16 rows that start on a 16-byte boundary are read eight elements at a time.
 template <>
 __device__ __forceinline__ float warp_dot<bf16>(const bf16* __restrict__ weights, const float* __restrict__ vector, int length, int lane) {
     float sum = 0.0f;
     if ((reinterpret_cast<uintptr_t>(weights) & 15) == 0 && length % 8 == 0) {
-        for (int column = lane * 8; column < length; column += 256) {
-            const uint4 raw = *reinterpret_cast<const uint4*>(weights + column);
-            const unsigned words[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                sum = fmaf(__uint_as_float(words[i] << 16), vector[column + 2 * i], sum);
-                sum = fmaf(__uint_as_float(words[i] & 0xffff0000u), vector[column + 2 * i + 1], sum);
-            }
-        }
+        for (int column = lane * 8; column < length; column += 256) sum += dot8(*reinterpret_cast<const uint4*>(weights + column), vector + column);
     } else {
         for (int column = lane; column < length; column += 32) sum = fmaf(__bfloat162float(weights[column]), vector[column], sum);
     }
@@ -52,17 +83,6 @@ __device__ __forceinline__ void warp_dot_pair(const T* __restrict__ first, const
     second_sum = warp_dot(second, second_vector, length, lane);
 }
 
-__device__ __forceinline__ float dot8(const uint4& raw, const float* __restrict__ vector) {
-    const unsigned words[4] = {raw.x, raw.y, raw.z, raw.w};
-    float sum = 0.0f;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        sum = fmaf(__uint_as_float(words[i] << 16), vector[2 * i], sum);
-        sum = fmaf(__uint_as_float(words[i] & 0xffff0000u), vector[2 * i + 1], sum);
-    }
-    return sum;
-}
-
 template <>
 __device__ __forceinline__ void warp_dot_pair<bf16>(const bf16* __restrict__ first, const float* __restrict__ first_vector, const bf16* __restrict__ second,
                                                     const float* __restrict__ second_vector, int length, int lane, float& first_sum, float& second_sum) {
@@ -73,6 +93,18 @@ __device__ __forceinline__ void warp_dot_pair<bf16>(const bf16* __restrict__ fir
     }
     float a = 0.0f, b = 0.0f, c = 0.0f, d = 0.0f;
     int column = lane * 8;
+    for (; column + 768 < length; column += 1024) {      // eight loads in flight
+        uint4 x[4], y[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            x[i] = *reinterpret_cast<const uint4*>(first + column + 256 * i);
+            y[i] = *reinterpret_cast<const uint4*>(second + column + 256 * i);
+        }
+        a += dot8(x[0], first_vector + column) + dot8(x[2], first_vector + column + 512);
+        b += dot8(y[0], second_vector + column) + dot8(y[2], second_vector + column + 512);
+        c += dot8(x[1], first_vector + column + 256) + dot8(x[3], first_vector + column + 768);
+        d += dot8(y[1], second_vector + column + 256) + dot8(y[3], second_vector + column + 768);
+    }
     for (; column + 256 < length; column += 512) {
         const uint4 a0 = *reinterpret_cast<const uint4*>(first + column), b0 = *reinterpret_cast<const uint4*>(second + column);
         const uint4 a1 = *reinterpret_cast<const uint4*>(first + column + 256), b1 = *reinterpret_cast<const uint4*>(second + column + 256);
@@ -97,7 +129,7 @@ moe_route_kernel(const T* __restrict__ hidden, const float* __restrict__ router,
                  int width, int experts, int top, int softmax, int renormalize) {
     grid_dependents_launch();
     grid_dependency_wait();
-    extern __shared__ float shared[];
+    extern __shared__ __align__(16) float shared[];
     float* row = shared;               // [width]
     float* scores = shared + width;    // [experts]
     float* choice = scores + experts;  // [experts]
@@ -161,7 +193,7 @@ moe_gate_up_kernel(const T* __restrict__ hidden, const T* __restrict__ gate_up, 
                    int width, int inner, int top, int features_per_block, int interleave) {
     grid_dependents_launch();
     grid_dependency_wait();
-    extern __shared__ float row[];
+    extern __shared__ __align__(16) float row[];
     const int pair = blockIdx.x, token = pair / top, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     for (int column = threadIdx.x; column < width; column += blockDim.x) row[column] = to_float(hidden[static_cast<size_t>(token) * width + column]);
     __syncthreads();
@@ -185,7 +217,7 @@ moe_down_kernel(const T* __restrict__ inner_in, const T* __restrict__ down, cons
                 int features_per_block) {
     grid_dependents_launch();
     grid_dependency_wait();
-    extern __shared__ float rows[];     // [top][inner]
+    extern __shared__ __align__(16) float rows[];     // [top][inner]
     const int token = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     for (int item = threadIdx.x; item < top * inner; item += blockDim.x) rows[item] = to_float(inner_in[static_cast<size_t>(token) * top * inner + item]);
     __syncthreads();
@@ -284,7 +316,7 @@ int launch_all(int what, const void* a, const void* b, const void* c, const void
         tau_launch(moe_gate_up_kernel<T>, dim3(tokens * top, (inner + per_block - 1) / per_block), dim3(kThreads), bytes, s, static_cast<const T*>(a),
                    static_cast<const T*>(b), static_cast<const int*>(c), static_cast<T*>(o1), width, inner, top, per_block, flag_a);
     } else {
-        const int per_block = 64;
+        const int per_block = tokens * ((width + 63) / 64) >= 1024 ? 64 : tokens * ((width + 31) / 32) >= 1024 ? 32 : 16;   // few tokens: smaller tiles, more blocks
         const size_t bytes = static_cast<size_t>(top) * inner * sizeof(float);
         if (bytes > 48 * 1024 && cudaFuncSetAttribute(moe_down_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes)) != cudaSuccess)
             return cudaErrorInvalidValue;

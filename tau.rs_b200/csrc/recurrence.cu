@@ -28,6 +28,18 @@ constexpr int kColumns = 32;                                                    
 
 __device__ __forceinline__ float activate(float value, int activation) { return activation ? value / (1.0f + expf(-value)) : value; }
 
+// The gates' pre-activations become log gates in place, for all tokens at once: what does not depend on the token before
+// is not computed inside the walk.  gates [tokens, 2 heads]: inputs first, then forgets.
+__global__ void log_gates_kernel(float* __restrict__ gates, long long count, int heads, float gate_cap) {
+    grid_dependents_launch();
+    grid_dependency_wait();
+    for (long long index = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; index < count; index += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const float capped = gate_cap * tanhf(gates[index] / gate_cap);
+        const bool forget = (index / heads) & 1;
+        gates[index] = forget ? fminf(capped, 0.0f) - log1pf(expf(-fabsf(capped))) : capped;     // logsigmoid for the forget gate
+    }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kColumns * kSplit)
 linear_recurrence_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, long long stride,
@@ -95,9 +107,7 @@ linear_recurrence_kernel(const T* __restrict__ q, const T* __restrict__ k, const
         if (token + 1 < end) fetch(token + 1);
         float keep = decay, take = 1.0f;
         if (exponential) {
-            const float log_in = gate_cap * tanhf(raw_in / gate_cap);
-            const float capped = gate_cap * tanhf(raw_forget / gate_cap);
-            const float log_forget = fminf(capped, 0.0f) - log1pf(expf(-fabsf(capped)));     // logsigmoid
+            const float log_in = raw_in, log_forget = raw_forget;     // made log gates by `log_gates_kernel`
             const float m_new = fmaxf(log_forget + m, log_in);
             keep = expf(log_forget + m - m_new);
             take = expf(log_in - m_new);
@@ -144,11 +154,12 @@ linear_recurrence_kernel(const T* __restrict__ q, const T* __restrict__ k, const
 
 TAU_EXPORT int tau_recurrence_key_dim() { return kDim; }
 
-// q, k, v: rows `stride` elements apart, heads side by side.  gates [tokens, 2 heads] (exponential) or decays [heads].
+// q, k, v: rows `stride` elements apart, heads side by side.  gates [tokens, 2 heads] (exponential; pre-activations, turned into log
+// gates in place) or decays [heads].
 // state: records `slot_stride` floats apart per slot.  out [tokens, heads * value_dim], 32-bit.
-TAU_EXPORT int tau_linear_recurrence(int dtype, const void* q, const void* k, const void* v, long long stride, const float* gates,
+TAU_EXPORT int tau_linear_recurrence(int dtype, const void* q, const void* k, const void* v, long long stride, float* gates,
                                      const float* decays, float* state, long long slot_stride, const int* cu_seqlens, const int* seq_slot,
-                                     float* out, int n_seqs, int heads, int value_dim, int exponential, float gate_cap, float query_scale,
+                                     float* out, int tokens, int n_seqs, int heads, int value_dim, int exponential, float gate_cap, float query_scale,
                                      int activation, void* stream) {
     if (n_seqs <= 0) return 0;
     if (!q || !k || !v || !state || !cu_seqlens || !seq_slot || !out || heads <= 0 || value_dim <= 0 || (exponential ? !gates : !decays))
@@ -156,6 +167,13 @@ TAU_EXPORT int tau_linear_recurrence(int dtype, const void* q, const void* k, co
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const int tile = exponential ? kColumns - 1 : kColumns;
     dim3 grid(heads, n_seqs, (value_dim + tile - 1) / tile), block(kColumns * kSplit);
+    if (exponential) {
+        if (tokens <= 0) return cudaErrorInvalidValue;
+        const long long count = static_cast<long long>(tokens) * 2 * heads;
+        tau_launch(log_gates_kernel, dim3(static_cast<unsigned>((count + 255) / 256 < 1184 ? (count + 255) / 256 : 1184)), dim3(256), 0, s, gates, count, heads, gate_cap);
+        const int status = tau_launch_status();
+        if (status != 0) return status;
+    }
     if (dtype == TAU_F32)
         tau_launch(linear_recurrence_kernel<float>, grid, block, 0, s, static_cast<const float*>(q), static_cast<const float*>(k), static_cast<const float*>(v),
                    stride, gates, decays, state, slot_stride, cu_seqlens, seq_slot, out, heads, value_dim, exponential, gate_cap, query_scale, activation);

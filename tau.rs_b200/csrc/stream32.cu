@@ -69,17 +69,39 @@ gated_group_norm_kernel(const float* __restrict__ values, const float* __restric
     const int row = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
     const int width = groups * group_width;
     const float* source = values + static_cast<size_t>(row) * width;
-    for (int group = warp; group < groups; group += warps) {
+    __shared__ float scratch[33];
+    if (groups >= warps) {       // many groups: a warp takes a group at a time
+        for (int group = warp; group < groups; group += warps) {
+            float inverse = 1.0f;
+            if (normalize) {
+                float squares = 0.0f;
+                for (int column = lane; column < group_width; column += 32) {
+                    const float value = source[group * group_width + column];
+                    squares += value * value;
+                }
+                inverse = 1.0f / sqrtf(warp_sum(squares) / static_cast<float>(group_width) + eps);
+            }
+            for (int column = lane; column < group_width; column += 32) {
+                const int index = group * group_width + column;
+                float value = source[index] * inverse;
+                if (weight) value *= weight[index];
+                if (gate) value *= 1.0f / (1.0f + expf(-to_float(gate[static_cast<size_t>(row) * gate_stride + index])));
+                out[static_cast<size_t>(row) * width + index] = from_float<T>(value);
+            }
+        }
+        return;
+    }
+    for (int group = 0; group < groups; ++group) {     // few groups: the whole block takes one after the other
         float inverse = 1.0f;
         if (normalize) {
             float squares = 0.0f;
-            for (int column = lane; column < group_width; column += 32) {
+            for (int column = threadIdx.x; column < group_width; column += blockDim.x) {
                 const float value = source[group * group_width + column];
                 squares += value * value;
             }
-            inverse = 1.0f / sqrtf(warp_sum(squares) / static_cast<float>(group_width) + eps);
+            inverse = 1.0f / sqrtf(block_sum(squares, scratch) / static_cast<float>(group_width) + eps);
         }
-        for (int column = lane; column < group_width; column += 32) {
+        for (int column = threadIdx.x; column < group_width; column += blockDim.x) {
             const int index = group * group_width + column;
             float value = source[index] * inverse;
             if (weight) value *= weight[index];
@@ -117,7 +139,7 @@ TAU_EXPORT int tau_gated_group_norm(int dtype, const float* values, const float*
     if (rows <= 0) return 0;
     if (!values || !out || groups <= 0 || group_width <= 0) return cudaErrorInvalidValue;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    const int threads = groups >= 8 ? 256 : groups * 32 < 64 ? 64 : groups * 32;
+    const int threads = 256;
     if (dtype == TAU_F32) tau_launch(gated_group_norm_kernel<float>, dim3(rows), dim3(threads), 0, s, values, weight, static_cast<const float*>(gate), gate_stride, static_cast<float*>(out), groups, group_width, eps, normalize);
     else if (dtype == TAU_BF16) tau_launch(gated_group_norm_kernel<bf16>, dim3(rows), dim3(threads), 0, s, values, weight, static_cast<const bf16*>(gate), gate_stride, static_cast<bf16*>(out), groups, group_width, eps, normalize);
     else return cudaErrorInvalidValue;
