@@ -1044,21 +1044,59 @@ TAU_EXPORT int tau_gemm_tc(int out_dtype, const void* x, const void* w, const fl
 
 // One product per group of consecutive rows, each with a weight of its own: rows bounds[g] .. bounds[g + 1] of `x` (and of
 // `out`) meet the weight `w + g * w_group` (elements).  `bounds` is host memory, `groups + 1` ascending row numbers.  The
-// products are launched one after another from here, which costs a fraction of a launch through a foreign-function call each.
+// products are launched from here, which costs a fraction of a launch through a foreign-function call each.  They are
+// independent of one another and each fills only part of the machine when its group is small, so they are dealt round to
+// `kGroupStreams` streams of this library's own, which wait for the caller's stream first and which it waits for afterwards.
+// A product on such a stream is not cut along K: the workspace of the cut is one per stream order.
+namespace {
+constexpr int kGroupStreams = 4;
+cudaStream_t group_streams[kGroupStreams];
+cudaEvent_t group_fork, group_join[kGroupStreams];
+bool group_streams_ready = false;
+
+int prepare_group_streams() {
+    if (group_streams_ready) return 0;
+    if (cudaEventCreateWithFlags(&group_fork, cudaEventDisableTiming) != cudaSuccess) return cudaErrorUnknown;
+    for (int i = 0; i < kGroupStreams; ++i) {
+        if (cudaStreamCreateWithFlags(&group_streams[i], cudaStreamNonBlocking) != cudaSuccess) return cudaErrorUnknown;
+        if (cudaEventCreateWithFlags(&group_join[i], cudaEventDisableTiming) != cudaSuccess) return cudaErrorUnknown;
+    }
+    group_streams_ready = true;
+    return 0;
+}
+}  // namespace
+
 TAU_EXPORT int tau_gemm_tc_groups(int out_dtype, const void* x, const void* w, void* out, const int* bounds, int groups, int N, int K,
                                   long long x_stride, long long w_stride, long long out_stride, long long w_group, int gated, void* workspace,
                                   long long workspace_floats, void* tickets, void* stream) {
     if (!bounds || groups <= 0) return cudaErrorInvalidValue;
-    const size_t out_bytes = out_dtype == TAU_F32 ? 4 : 2;
-    for (int group = 0; group < groups; ++group) {
-        const int begin = bounds[group], rows = bounds[group + 1] - begin;
-        if (rows < 0) return cudaErrorInvalidValue;
-        if (rows == 0) continue;
-        const int status = tau_gemm_tc(out_dtype, static_cast<const bf16*>(x) + static_cast<size_t>(begin) * x_stride,
-                                       static_cast<const bf16*>(w) + static_cast<size_t>(group) * w_group, nullptr,
-                                       static_cast<char*>(out) + static_cast<size_t>(begin) * out_stride * out_bytes, rows, N, K, x_stride, w_stride,
-                                       out_stride, 0, gated, 0, workspace, workspace_floats, tickets, -1, 1, stream);
-        if (status != 0) return status;
+    cudaStream_t caller = static_cast<cudaStream_t>(stream);
+    cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+    cudaStreamIsCapturing(caller, &capturing);
+    const bool spread = groups > 1 && capturing == cudaStreamCaptureStatusNone && prepare_group_streams() == 0;
+    if (spread) {
+        if (cudaEventRecord(group_fork, caller) != cudaSuccess) return cudaErrorUnknown;
+        for (int i = 0; i < kGroupStreams; ++i)
+            if (cudaStreamWaitEvent(group_streams[i], group_fork, 0) != cudaSuccess) return cudaErrorUnknown;
     }
-    return 0;
+    const size_t out_bytes = out_dtype == TAU_F32 ? 4 : 2;
+    int result = 0, launched = 0;
+    for (int group = 0; group < groups && result == 0; ++group) {
+        const int begin = bounds[group], rows = bounds[group + 1] - begin;
+        if (rows < 0) { result = cudaErrorInvalidValue; break; }
+        if (rows == 0) continue;
+        result = tau_gemm_tc(out_dtype, static_cast<const bf16*>(x) + static_cast<size_t>(begin) * x_stride,
+                             static_cast<const bf16*>(w) + static_cast<size_t>(group) * w_group, nullptr,
+                             static_cast<char*>(out) + static_cast<size_t>(begin) * out_stride * out_bytes, rows, N, K, x_stride, w_stride,
+                             out_stride, 0, gated, spread ? 1 : 0, workspace, workspace_floats, tickets, -1, 1,
+                             spread ? static_cast<void*>(group_streams[launched % kGroupStreams]) : stream);
+        ++launched;
+    }
+    if (spread) {   // the caller's stream goes on only when every product has finished, also after an error
+        for (int i = 0; i < kGroupStreams; ++i) {
+            if (cudaEventRecord(group_join[i], group_streams[i]) != cudaSuccess || cudaStreamWaitEvent(caller, group_join[i], 0) != cudaSuccess)
+                return result != 0 ? result : cudaErrorUnknown;
+        }
+    }
+    return result;
 }
