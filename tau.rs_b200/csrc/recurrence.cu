@@ -24,7 +24,7 @@ namespace {
 constexpr int kDim = TAU_KEY_DIM;
 constexpr int kSplit = kDim <= 16 ? 1 : kDim <= 32 ? 2 : kDim <= 64 ? 4 : kDim <= 128 ? 8 : kDim <= 256 ? 16 : 32;   // threads that share a column
 constexpr int kRows = (kDim + kSplit - 1) / kSplit;                               // key rows per thread
-constexpr int kColumns = 32;                                                      // columns of a block (n included)
+// Columns of a block (n included): 32, or 16 where 32 would leave SMs without a block.
 
 __device__ __forceinline__ float activate(float value, int activation) { return activation ? value / (1.0f + expf(-value)) : value; }
 
@@ -40,7 +40,7 @@ __global__ void log_gates_kernel(float* __restrict__ gates, long long count, int
     }
 }
 
-template <typename T>
+template <typename T, int kColumns>
 __global__ void __launch_bounds__(kColumns * kSplit)
 linear_recurrence_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, long long stride,
                          const float* __restrict__ gates, const float* __restrict__ decays, float* __restrict__ state, long long slot_stride,
@@ -48,7 +48,7 @@ linear_recurrence_kernel(const T* __restrict__ q, const T* __restrict__ k, const
                          int heads, int value_dim, int exponential, float gate_cap, float query_scale, int activation) {
     grid_dependents_launch();
     grid_dependency_wait();
-    __shared__ float qs[2][kDim], ks[2][kDim], partial[kSplit][kColumns], scalars[2];
+    __shared__ float qs[2][kDim], ks[2][kDim], partial[2][kSplit][kColumns];
     const int head = blockIdx.x, sequence = blockIdx.y;
     const int columns = value_dim + (exponential ? 1 : 0);           // n rides as one more column of the state
     // A block serves a tile of value columns; with the exponential gating its last thread column serves n as well, in every
@@ -123,24 +123,23 @@ linear_recurrence_kernel(const T* __restrict__ q, const T* __restrict__ k, const
                 sums[r & 3] = fmaf(S[r], qs[half][row0 + r], sums[r & 3]);
             }
         }
-        float sum = (sums[0] + sums[1]) + (sums[2] + sums[3]);
-        if (kSplit > 1) {
-            partial[part][local] = sum;
-            __syncthreads();
-            sum = 0.0f;
+        // One barrier per token: partial sums and the next token's q and k go to the halves of shared memory that nobody reads
+        // now; behind the barrier the first thread of each column adds the parts up, and n's as well for the denominator.
+        partial[half][part][local] = (sums[0] + sums[1]) + (sums[2] + sums[3]);
+        if (token + 1 < end) publish(half ^ 1);
+        __syncthreads();
+        if (part == 0 && live && !is_n) {
+            float sum = 0.0f;
 #pragma unroll
-            for (int p = 0; p < kSplit; ++p) sum += partial[p][local];
+            for (int p = 0; p < kSplit; ++p) sum += partial[half][p][local];
+            if (exponential) {
+                float normaliser = 0.0f;
+#pragma unroll
+                for (int p = 0; p < kSplit; ++p) normaliser += partial[half][p][kColumns - 1];
+                sum /= fmaxf(fabsf(normaliser), expf(-m)) + 1e-6f;
+            }
+            out[static_cast<size_t>(token) * heads * value_dim + head * value_dim + column] = sum;
         }
-        if (exponential) {
-            if (is_n && part == 0) scalars[half] = fmaxf(fabsf(sum), expf(-m)) + 1e-6f;
-            if (token + 1 < end) publish(half ^ 1);
-            __syncthreads();
-            sum /= scalars[half];
-        } else {
-            if (token + 1 < end) publish(half ^ 1);
-            __syncthreads();
-        }
-        if (live && !is_n && part == 0) out[static_cast<size_t>(token) * heads * value_dim + head * value_dim + column] = sum;
     }
     if (live && (!is_n || blockIdx.z == 0)) {
 #pragma unroll
@@ -165,8 +164,6 @@ TAU_EXPORT int tau_linear_recurrence(int dtype, const void* q, const void* k, co
     if (!q || !k || !v || !state || !cu_seqlens || !seq_slot || !out || heads <= 0 || value_dim <= 0 || (exponential ? !gates : !decays))
         return cudaErrorInvalidValue;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    const int tile = exponential ? kColumns - 1 : kColumns;
-    dim3 grid(heads, n_seqs, (value_dim + tile - 1) / tile), block(kColumns * kSplit);
     if (exponential) {
         if (tokens <= 0) return cudaErrorInvalidValue;
         const long long count = static_cast<long long>(tokens) * 2 * heads;
@@ -174,13 +171,19 @@ TAU_EXPORT int tau_linear_recurrence(int dtype, const void* q, const void* k, co
         const int status = tau_launch_status();
         if (status != 0) return status;
     }
-    if (dtype == TAU_F32)
-        tau_launch(linear_recurrence_kernel<float>, grid, block, 0, s, static_cast<const float*>(q), static_cast<const float*>(k), static_cast<const float*>(v),
-                   stride, gates, decays, state, slot_stride, cu_seqlens, seq_slot, out, heads, value_dim, exponential, gate_cap, query_scale, activation);
-    else if (dtype == TAU_BF16)
-        tau_launch(linear_recurrence_kernel<bf16>, grid, block, 0, s, static_cast<const bf16*>(q), static_cast<const bf16*>(k), static_cast<const bf16*>(v),
-                   stride, gates, decays, state, slot_stride, cu_seqlens, seq_slot, out, heads, value_dim, exponential, gate_cap, query_scale, activation);
-    else
-        return cudaErrorInvalidValue;
+    const int wide = exponential ? 31 : 32;
+    const bool narrow = heads * n_seqs * ((value_dim + wide - 1) / wide) < 148 && kSplit <= 16;     // blocks of 16 columns reach more SMs
+    const int tile = narrow ? (exponential ? 15 : 16) : wide;
+    dim3 grid(heads, n_seqs, (value_dim + tile - 1) / tile), block((narrow ? 16 : 32) * kSplit);
+    if (dtype != TAU_F32 && dtype != TAU_BF16) return cudaErrorInvalidValue;
+#define TAU_RECURRENCE(T, COLUMNS)                                                                                                          \
+    tau_launch(linear_recurrence_kernel<T, COLUMNS>, grid, block, 0, s, static_cast<const T*>(q), static_cast<const T*>(k), static_cast<const T*>(v), \
+               stride, gates, decays, state, slot_stride, cu_seqlens, seq_slot, out, heads, value_dim, exponential, gate_cap, query_scale, activation)
+    if (dtype == TAU_F32) {
+        if (narrow) TAU_RECURRENCE(float, 16); else TAU_RECURRENCE(float, 32);
+    } else {
+        if (narrow) TAU_RECURRENCE(bf16, 16); else TAU_RECURRENCE(bf16, 32);
+    }
+#undef TAU_RECURRENCE
     return tau_launch_status();
 }

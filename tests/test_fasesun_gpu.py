@@ -253,6 +253,18 @@ def test_unequal_batches_against_each_request_alone(models, name, dtype):
     assert engine.cache.slots.in_use == 0
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_many_sequences_of_wide_heads(tmp_path, dtype):
+    """Enough (sequence, head, column tile) blocks that the state kernel takes its wider tiles; each request equals itself alone."""
+    cfg = fm.config([fm.mlstm(heads=3, dim=8, vdim=130, gate_cap=3.0, mlp=None), fm.lightning(heads=4, dim=24, vdim=70, mlp=None)], width=64, vocab=83)
+    values = fm.write_model(str(tmp_path), cfg, 9)
+    engine = Engine(load_model(str(tmp_path), dtype, "gpu"), 64 * 16)
+    requests = [tokens_for(cfg, 20 + 3 * index, 90 + index) for index in range(14)]
+    together = run_batched(engine, requests, [len(request) - 4 for request in requests])
+    for request, rows in zip(requests, together):
+        assert close(rows, plain_logits(cfg, values, request, dtype)[len(request) - 5 :], dtype)
+
+
 def test_slots_and_pages_that_are_used_again_start_clean(models):
     """A cache of three pages and as many slots: every request takes a slot whose state another left behind and pages that
     another wrote."""
