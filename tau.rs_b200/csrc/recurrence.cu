@@ -66,45 +66,53 @@ linear_recurrence_kernel(const T* __restrict__ q, const T* __restrict__ k, const
     float m = exponential ? record[static_cast<size_t>(columns) * kDim] : 0.0f;
     const float decay = exponential ? 1.0f : decays[head];
     const int begin = cu_seqlens[sequence], end = cu_seqlens[sequence + 1];
-    // The next token's q, k, v and gates are asked for before the current token is computed and put into the other half of
-    // qs/ks afterwards, so the walk along the sequence does not wait for memory at every token.
+    // Operands are asked for four tokens ahead, in four sets of registers that take turns: a token's q and k go into the free
+    // half of qs/ks one token before they are used, its v and gates stay in their set until its turn, and the set is filled
+    // again for the token four further on.  The walk then waits for memory at its start only.
     constexpr int kStage = (kDim + kColumns * kSplit - 1) / (kColumns * kSplit);
-    float next_q[kStage], next_k[kStage], next_v = 0.0f, next_in = 0.0f, next_forget = 0.0f;
-    auto fetch = [&](int token) {
+    constexpr int kAhead = 4;
+    float next_q[kAhead][kStage], next_k[kAhead][kStage], next_v[kAhead], next_in[kAhead], next_forget[kAhead];
+    auto fetch = [&](int set, int token) {
+        if (token >= end) return;
         const size_t row = static_cast<size_t>(token) * stride;
 #pragma unroll
         for (int i = 0; i < kStage; ++i) {
             const int d = threadIdx.x + i * kColumns * kSplit;
             if (d < kDim) {
-                next_q[i] = to_float(q[row + head * kDim + d]);
-                next_k[i] = to_float(k[row + head * kDim + d]);
+                next_q[set][i] = to_float(q[row + head * kDim + d]);
+                next_k[set][i] = to_float(k[row + head * kDim + d]);
             }
         }
-        if (live && !is_n) next_v = to_float(v[row + head * value_dim + column]);
+        if (live && !is_n) next_v[set] = to_float(v[row + head * value_dim + column]);
         if (exponential) {
-            next_in = gates[static_cast<size_t>(token) * 2 * heads + head];
-            next_forget = gates[static_cast<size_t>(token) * 2 * heads + heads + head];
+            next_in[set] = gates[static_cast<size_t>(token) * 2 * heads + head];
+            next_forget[set] = gates[static_cast<size_t>(token) * 2 * heads + heads + head];
         }
     };
-    auto publish = [&](int half) {
+    auto publish = [&](int set, int half) {
 #pragma unroll
         for (int i = 0; i < kStage; ++i) {
             const int d = threadIdx.x + i * kColumns * kSplit;
             if (d < kDim) {
-                qs[half][d] = activate(next_q[i], activation) * query_scale;
-                ks[half][d] = activate(next_k[i], activation);
+                qs[half][d] = activate(next_q[set][i], activation) * query_scale;
+                ks[half][d] = activate(next_k[set][i], activation);
             }
         }
     };
-    if (begin < end) {
-        fetch(begin);
-        publish(0);
+#pragma unroll
+    for (int set = 0; set < kAhead; ++set) {
+        next_v[set] = next_in[set] = next_forget[set] = 0.0f;
+        fetch(set, begin + set);
     }
+    if (begin < end) publish(0, 0);
     __syncthreads();
-    for (int token = begin; token < end; ++token) {
-        const int half = (token - begin) & 1;
-        const float raw_value = next_v, raw_in = next_in, raw_forget = next_forget;
-        if (token + 1 < end) fetch(token + 1);
+    for (int base = begin; base < end; base += kAhead) {
+#pragma unroll
+      for (int set = 0; set < kAhead; ++set) {
+        const int token = base + set;
+        if (token >= end) break;
+        const int half = set & 1;                  // kAhead is even: the halves take turns with the tokens
+        const float raw_value = next_v[set], raw_in = next_in[set], raw_forget = next_forget[set];
         float keep = decay, take = 1.0f;
         if (exponential) {
             const float log_in = raw_in, log_forget = raw_forget;     // made log gates by `log_gates_kernel`
@@ -126,7 +134,8 @@ linear_recurrence_kernel(const T* __restrict__ q, const T* __restrict__ k, const
         // One barrier per token: partial sums and the next token's q and k go to the halves of shared memory that nobody reads
         // now; behind the barrier the first thread of each column adds the parts up, and n's as well for the denominator.
         partial[half][part][local] = (sums[0] + sums[1]) + (sums[2] + sums[3]);
-        if (token + 1 < end) publish(half ^ 1);
+        if (token + 1 < end) publish((set + 1) % kAhead, half ^ 1);
+        fetch(set, token + kAhead);                 // this set's q and k were published a token ago, its v and gates just used
         __syncthreads();
         if (part == 0 && live && !is_n) {
             float sum = 0.0f;
@@ -140,6 +149,7 @@ linear_recurrence_kernel(const T* __restrict__ q, const T* __restrict__ k, const
             }
             out[static_cast<size_t>(token) * heads * value_dim + head * value_dim + column] = sum;
         }
+      }
     }
     if (live && (!is_n || blockIdx.z == 0)) {
 #pragma unroll
