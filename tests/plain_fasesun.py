@@ -79,6 +79,8 @@ def latent_attention(h: torch.Tensor, W: Dict[str, torch.Tensor], prefix: str, m
     v = linear(c, W[prefix + ".uv"], round_to).view(T, heads, vdim)
     scores = (torch.einsum("ihd,jhd->hij", q_plain, k_plain) + torch.einsum("ihd,jd->hij", q_rot, k_rot)) * mixer["scale"]
     causal = positions[None, :] <= positions[:, None]
+    if mixer.get("window"):          # not a part of Fasesun: a window that other designs may put on this mixer
+        causal = causal & (positions[None, :] > positions[:, None] - mixer["window"])
     scores = scores.masked_fill(~causal[None], float("-inf"))
     sink = W[prefix + ".sink"].to(h.dtype)                                           # [heads]; one more term of the denominator
     top = torch.maximum(scores.max(dim=-1).values, sink[:, None])

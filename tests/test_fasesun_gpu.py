@@ -351,3 +351,49 @@ def test_the_command_line_on_a_fasesun_folder(models, tmp_path):
     drawn = str(tmp_path / "drawn")
     records = run(["--random-weights", str(config_path), "--model", drawn, "--seed", "4", "--max-tokens", "5", "--stop-ids", "", "--prompt-ids", "1,2,3"])
     assert [len(record["tokens"]) for record in records if "tokens" in record] == [5]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_window_on_latent_attention_in_another_design(tmp_path, dtype):
+    """The mixer's spec takes a window that Fasesun never sets.  A toy architecture sets it: position i then sees the last 70
+    positions only, in whole prompts (the expanded form in bfloat16), in portions and in single tokens, and the cache gives the
+    pages back that fell out of it."""
+    import dataclasses
+
+    from tau_rs_b200.config import FasesunConfig, register_architecture
+    from tau_rs_b200.config.registry import unregister_architecture
+    from tau_rs_b200.models.fasesun import build_fasesun_spec
+
+    window = 70
+
+    def parse(raw):
+        return FasesunConfig.from_json(dict(raw, architecture="Fasesun"))
+
+    def build(config):
+        spec = build_fasesun_spec(config)
+        blocks = tuple(dataclasses.replace(block, mixer=dataclasses.replace(block.mixer, window=window)) for block in spec.blocks)
+        return dataclasses.replace(spec, architecture="WindowedLatentToy", blocks=blocks)
+
+    register_architecture("WindowedLatentToy", "windowedlatenttoy", parse, build, storage_dtype="bfloat16")
+    try:
+        layers = [fm.latent(heads=3, dim=16, rot_dim=16, vdim=24, q_rank=32, kv_rank=48, scale=1.5, mlp=None),
+                  fm.latent(heads=2, dim=24, rot_dim=16, vdim=8, q_rank=16, kv_rank=36, scale=1.0, mlp=None)]
+        cfg = dict(fm.config(layers, width=64, vocab=97), architecture="WindowedLatentToy")
+        values = fm.write_model(str(tmp_path), cfg, 17)
+        plain_cfg = {**cfg, "layers": [{**layer, "mixer": {**layer["mixer"], "window": window}} for layer in layers]}
+        tokens = tokens_for(cfg, 300, 18)
+        wanted = plain_logits(plain_cfg, values, tokens, dtype)
+        engine = Engine(load_model(str(tmp_path), dtype, "gpu"), 64 * 6)
+        assert close(run_whole(engine, tokens), wanted, dtype)
+        slot = engine.open_sequence()
+        found, position = [], 0
+        for count in [150, 3, 64, 2] + [1] * 81:
+            piece = tokens[position : position + count]
+            found.append(engine.step([StepEntry(slot, piece, list(range(count)))]).float().cpu().clone())
+            position += count
+            engine.cache.check()
+        assert position == 300 and all(len(group.held[slot]) <= 3 for group in engine.cache.kv.values())
+        engine.close_sequence(slot)
+        assert close(torch.cat(found), wanted, dtype)
+    finally:
+        unregister_architecture("WindowedLatentToy")
