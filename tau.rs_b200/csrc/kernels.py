@@ -795,7 +795,7 @@ def head_gate(values, gate, out, n_heads: int, width: int, value_dim: int) -> No
                                  ctypes.c_int(tokens), ctypes.c_int(n_heads), ctypes.c_int(width), ctypes.c_int(value_dim), _stream()), "latent_expand")
 
 
-LATENT_MAX_RANK = 512   # what the latent attention kernel keeps per lane
+LATENT_MAX_RANK = 1024   # what the latent attention kernel keeps per lane (rows of up to 768 elements take the vector form)
 
 
 _latent_scratch = {}

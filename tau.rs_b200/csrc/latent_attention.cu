@@ -14,7 +14,7 @@ namespace {
 
 constexpr int kTile = 32;          // cached positions per tile: one per lane
 constexpr int kMaxWarps = 8;       // heads per block
-constexpr int kMaxOwned = 16;      // latent columns per lane: rank <= 512
+constexpr int kMaxOwned = 32;      // latent columns per lane: rank <= 1024
 
 // One block per token.
 template <typename T>

@@ -61,9 +61,10 @@ def engine_of(models, name, dtype, max_tokens=1024):
 @pytest.mark.parametrize("layer", [
     fm.latent(mlp=None), fm.latent(heads=1, dim=8, rot_dim=24, rot_dims=12, vdim=8, q_rank=16, kv_rank=16, scale=0.9, mlp=None),
     fm.latent(heads=3, dim=32, rot_dim=16, rot_dims=16, vdim=40, q_rank=24, kv_rank=56, mlp=None),
+    fm.latent(heads=2, dim=16, rot_dim=16, vdim=16, q_rank=16, kv_rank=800, mlp=None),
     fm.mlstm(mlp=None), fm.mlstm(heads=3, dim=8, vdim=130, gate_cap=2.0, mlp=None),
     fm.lightning(mlp=None), fm.lightning(heads=2, dim=100, vdim=12, decay=[0.3, 1.0], mlp=None),
-], ids=["latent", "latent_one_head", "latent_expanding", "mlstm", "mlstm_wide_values", "lightning", "lightning_wide_keys"])
+], ids=["latent", "latent_one_head", "latent_expanding", "latent_wide_rank", "mlstm", "mlstm_wide_values", "lightning", "lightning_wide_keys"])
 def test_a_mixer_alone(tmp_path, layer, dtype):
     cfg = fm.config([layer], width=80, vocab=61)
     values = fm.write_model(str(tmp_path), cfg, 5)
