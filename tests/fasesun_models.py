@@ -50,6 +50,12 @@ ODD = config([mlstm(heads=1, dim=16, vdim=150, gate_cap=4.0, mlp=moe(experts=1, 
 PEAKY = config([latent(heads=3, dim=16, rot_dim=16, vdim=24, q_rank=32, kv_rank=48, scale=2.5, mlp=None)], width=64, vocab=97)
 
 
+# Nothing a multiple of 8: rows that no 16-byte load can take, products that no tensor-core tile fits.
+RAGGED = config([latent(heads=3, dim=12, rot_dim=6, vdim=10, q_rank=20, kv_rank=30, mlp=moe(experts=5, top=2, ff=20, shared_ff=12)),
+                 mlstm(heads=2, dim=12, vdim=10, mlp=moe(experts=5, top=2, ff=20, shared_ff=12)),
+                 lightning(heads=2, dim=10, vdim=6, mlp=None)], width=100, vocab=77, loop=(0, 2, 2))
+
+
 def weights(cfg: dict, seed: int) -> Dict[str, torch.Tensor]:
     """Random weights of the scales that keep every branch alive, every value one that bfloat16 holds."""
     generator = torch.Generator().manual_seed(seed)

@@ -19,7 +19,7 @@ def test_the_short_spelling_of_the_architecture_is_read():
     assert architecture_for(fm.MIXED).storage_dtype == "bfloat16"
 
 
-@pytest.mark.parametrize("cfg", [fm.MIXED, fm.ODD, fm.PEAKY])
+@pytest.mark.parametrize("cfg", [fm.MIXED, fm.ODD, fm.PEAKY, fm.RAGGED])
 def test_layer_runs_follow_the_loop(cfg):
     config = FasesunConfig.from_json(cfg)
     assert list(config.layer_runs()) == list(plain_fasesun.layer_runs(cfg))

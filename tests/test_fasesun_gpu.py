@@ -45,7 +45,7 @@ def plain_logits(cfg, values, tokens, dtype):
 def models(tmp_path_factory):
     root = tmp_path_factory.mktemp("fasesun")
     made = {}
-    for name, cfg, seed in (("mixed", fm.MIXED, 11), ("odd", fm.ODD, 12), ("peaky", fm.PEAKY, 13)):
+    for name, cfg, seed in (("mixed", fm.MIXED, 11), ("odd", fm.ODD, 12), ("peaky", fm.PEAKY, 13), ("ragged", fm.RAGGED, 14)):
         folder = str(root / name)
         made[name] = (folder, cfg, fm.write_model(folder, cfg, seed))
     return made
@@ -199,7 +199,7 @@ def test_products_of_a_batch_of_heads():
 
 # ---- whole models: cuttings, batches, reuse --------------------------------------------------------------------------
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["mixed", "odd"])
+@pytest.mark.parametrize("name", ["mixed", "odd", "ragged"])
 def test_whole_prompts_single_tokens_and_the_first_positions(models, name, dtype):
     engine, cfg, values = engine_of(models, name, dtype)
     tokens = tokens_for(cfg, 200, 21)
@@ -241,7 +241,7 @@ def test_a_sharp_softmax_loses_no_key_far_away_or_at_a_page_border(models, dtype
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["mixed", "odd", "peaky"])
+@pytest.mark.parametrize("name", ["mixed", "odd", "peaky", "ragged"])
 def test_unequal_batches_against_each_request_alone(models, name, dtype):
     engine, cfg, values = engine_of(models, name, dtype, 2048)
     lengths, prompts = [90, 31, 140, 5, 66], [70, 1, 129, 3, 64]
