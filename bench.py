@@ -285,13 +285,14 @@ def fasesun_sizes():
         return dict(qwen3(4, width, heads, 8, intermediate, True), vocab_size=32768)
 
     return {
+        "1024": (fasesun(1024, 8, 384, 2, 704, 1408), dense(1024, 8, 6 * 704 + 1408)),
         "2048": (fasesun(2048, 16, 768, 4, 1408, 2816), dense(2048, 16, 6 * 1408 + 2816)),
         "4096": (fasesun(4096, 32, 1536, 8, 2048, 4096), dense(4096, 32, 6 * 2048 + 4096)),
     }
 
 
 def design_comparison(args) -> int:
-    """`--design fasesun`: prefill and decode throughput of Fasesun layers at two real sizes beside a dense Qwen3 of equal width,
+    """`--design fasesun`: prefill and decode throughput of Fasesun layers at three real sizes beside a dense Qwen3 of equal width,
     depth and active feed-forward width, with the device time of each kernel class in one prompt step and one decode step."""
     import numpy as np
     import torch
