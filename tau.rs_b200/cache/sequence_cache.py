@@ -29,7 +29,7 @@ holds about `window / 64 + 2` pages however long it grows.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass
+from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Tuple
 
 import numpy as np
@@ -51,6 +51,7 @@ class KVLayerView:
     values: torch.Tensor
     group: str                # key of the step's page rows (`StepContext.page_rows[group]`)
     window: Optional[int]
+    extra: Dict[str, object] = field(default_factory=dict)   # role -> view of what the block keeps beside this (`ScheduleEntry.extra_cache`)
 
 
 @dataclass
@@ -58,11 +59,13 @@ class RowsLayerView:
     rows: torch.Tensor        # [pages, PAGE_TOKENS, row_width]
     group: str
     window: Optional[int]
+    extra: Dict[str, object] = field(default_factory=dict)
 
 
 @dataclass
 class StateLayerView:
     state: torch.Tensor       # [slots, *shape]
+    extra: Dict[str, object] = field(default_factory=dict)
 
 
 class _KVGroup:

@@ -5,5 +5,6 @@ from .qwen3 import Qwen3Config
 from .registry import (Architecture, architecture_for, register_architecture, registered_architectures,
                        spec_from_config_json, unregister_architecture)
 from .fasesun import FasesunConfig
-from .specs import (AttentionSpec, BlockSpec, LatentAttentionSpec, LinearRecurrenceSpec, ModelSpec, NormSpec, PairRotationSpec,
-                    PositionSpec, RoutedExpertsSpec, ScheduleEntry, SwiGLUSpec)
+from .bisudra import BisudraConfig
+from .specs import (AttentionSpec, BlockSpec, DenseFeedForwardSpec, DifferentialAttentionSpec, LatentAttentionSpec, LinearRecurrenceSpec, ModelSpec, NormSpec, PairRotationSpec,
+                    PositionSpec, RoutedExpertsSpec, ScheduleEntry, SublayerNormBlockSpec, SwiGLUSpec, TokenSideSpec)

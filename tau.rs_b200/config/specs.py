@@ -15,9 +15,13 @@ from typing import Optional, Tuple
 
 @dataclass(frozen=True)
 class NormSpec:
+    """`kind == "rms_norm"`: `x / sqrt(mean(x^2) + eps) * w`.  `kind == "layer_norm"`: `(x - mean) / sqrt(variance + eps) * w + b`,
+    the bias being the tensor `<weight's name><bias_suffix>`."""
+
     width: int
     eps: float
     kind: str = "rms_norm"
+    bias_suffix: str = ".bias"
 
 
 @dataclass(frozen=True)
@@ -90,6 +94,58 @@ class LatentAttentionSpec:
 
 
 @dataclass(frozen=True)
+class DifferentialAttentionSpec:
+    """Softmax attention with two maps per head: each head has two queries and each key/value head two keys of `dim` elements
+    (laid out head by head as [map 1, map 2]) over one value of `value_dim` elements; a head's result is
+    `map 1 - lambda * map 2` with `lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + diff` (four learned vectors of `dim` elements, one
+    number for the layer), divided by its root mean square over `value_dim` (eps inside the root, no weight), times `1 - diff`.
+    Queries and keys pass an RMS norm over `dim` whose weight all heads and maps share, then `position`; `window` limits how far
+    back a query sees (itself and the `window - 1` positions before it); `gate` multiplies the heads by a sigmoid of one more
+    projection of the input before the output projection."""
+
+    hidden: int
+    n_heads: int
+    n_kv_heads: int
+    dim: int
+    value_dim: int
+    softmax_scale: float
+    diff: float
+    eps: float
+    position: Optional[PairRotationSpec] = None
+    window: Optional[int] = None
+    gate: bool = True
+    kind: str = "differential_attention"
+
+
+@dataclass(frozen=True)
+class DenseFeedForwardSpec:
+    """`down(act(up(x) + b_up)) + b_down` with `act` one of "relu_squared".  Tensors `<prefix>.<name><weight_suffix>` and, with
+    `bias`, `<prefix>.<name><bias_suffix>`."""
+
+    hidden: int
+    intermediate: int
+    activation: str = "relu_squared"
+    bias: bool = True
+    up_name: str = "up"
+    down_name: str = "down"
+    weight_suffix: str = ""
+    bias_suffix: str = ".b"
+    kind: str = "dense_mlp"
+
+
+@dataclass(frozen=True)
+class TokenSideSpec:
+    """A per-layer input looked up by token id: `e` = columns `offset .. offset + dim` of the model's shared table `table`
+    ([vocab, table_width]) at the token; `y = proj(gelu_tanh(gate(x)) * e)`; `x <- x + y / sqrt(mean(y^2) + eps) * w`."""
+
+    table: str
+    table_width: int
+    offset: int
+    dim: int
+    eps: float
+
+
+@dataclass(frozen=True)
 class LinearRecurrenceSpec:
     """A matrix state per head, `S_t = a_t S_(t-1) + b_t k_t v_t^T`, read as `S_t^T q_t`.
 
@@ -117,7 +173,8 @@ class LinearRecurrenceSpec:
 class RoutedExpertsSpec:
     """`top` of `experts` gated feed-forwards per token.  The router's logits pass through `score` ("sigmoid" or
     "softmax"); experts are chosen by score plus a correction per expert (if `correction`), weighted by the score itself,
-    renormalised over the chosen ones only if `renormalize`.  `shared` is a feed-forward that every token passes; with
+    renormalised over the chosen ones only if `renormalize` (a softmax score renormalised is the softmax over the chosen logits
+    alone).  `router_bias` adds the tensor `<prefix>.router.b` to the logits.  `shared` is a feed-forward that every token passes; with
     `shared_gate` its output is scaled by the sigmoid of one more projection of the token."""
 
     hidden: int
@@ -130,6 +187,7 @@ class RoutedExpertsSpec:
     shared: Optional[SwiGLUSpec] = None
     shared_gate: bool = False
     kind: str = "routed_experts"
+    router_bias: bool = False
 
 
 @dataclass(frozen=True)
@@ -142,6 +200,29 @@ class BlockSpec:
     mixer_norm: NormSpec
     feed_forward_norm: Optional[NormSpec]
     kind: str = "pre_norm"
+
+
+@dataclass(frozen=True)
+class SublayerNormBlockSpec:
+    """One layer whose norms act on what a sublayer returns: `x <- x + norm(gate * mixer(read(x)))`, then the same with the
+    feed-forward (absent if `feed_forward` is None), on a residual stream kept in 32-bit; both sublayers read `x` itself.
+
+    `input_taps` > 0: the mixer reads `x + conv(x)`, a causal convolution of that many taps over time on each channel, whose last
+    `input_taps - 1` inputs are state of the sequence.  `residual_gate`: each sublayer's result is multiplied by
+    `sigmoid(W x + b)` before its norm.  `token_side`: a per-layer input by token id joins the stream after the feed-forward.
+    `depth_mix` = n > 0: what the block hands on is `sum_j w[j] * X_j` over the model's first n results (`X_0` the embedding
+    output, `X_(k+1)` what run k of the schedule produced before this mixing), n being this run's index plus 2."""
+
+    prefix: str
+    mixer: object
+    feed_forward: object
+    mixer_norm: NormSpec
+    feed_forward_norm: Optional[NormSpec]
+    input_taps: int = 0
+    residual_gate: bool = False
+    token_side: Optional[TokenSideSpec] = None
+    depth_mix: int = 0
+    kind: str = "sublayer_norm"
 
 
 @dataclass(frozen=True)
@@ -159,6 +240,8 @@ class ScheduleEntry:
     cache_group: Optional[str] = None
     cache_layer: int = 0
     writes_cache: bool = True
+    # What the block keeps beside its mixer's cache (`Block.extra_cache_needs()`): (role, cache group, cache layer) for each role.
+    extra_cache: Tuple[Tuple[str, str, int], ...] = ()
 
 
 @dataclass(frozen=True)
@@ -181,3 +264,9 @@ class ModelSpec:
     input_position: Optional[object] = None
     # "float32": the residual stream is kept in 32-bit whatever the run's dtype (None: in the run's dtype).
     residual_dtype: Optional[str] = None
+    # The model keeps the embedding output and the result of every run of the schedule for the step's tokens
+    # (`StepContext.results` [runs + 1, tokens, hidden]; `StepContext.run` is the index of the run that is being computed).
+    keeps_results: bool = False
+    # Tensors that belong to no single block: (name, shape, role).  The model reads them and hands each to the blocks that
+    # list its name in `shared_tensor_names()`.
+    shared_tensors: Tuple[Tuple[str, Tuple[int, ...], str], ...] = ()

@@ -1,0 +1,204 @@
+// Differential attention over cached rows: every head has two softmax maps (each with its own query and key of `dim` elements)
+// over the same values of `vdim` elements, combined as a1 - lambda * a2, divided by the root mean square over the head's values,
+// scaled, and gated by a sigmoid.
+//
+// One cached row per position: [kv_heads x (map 1 key | map 2 key) | kv_heads x value], keys normalised and rotated already.
+//
+//   prepare:    per (head, map): q and k divided by their root mean square over `dim` (eps inside the root), times a weight shared
+//               by all heads and maps, the first `rotary` elements turned pair by pair (2i, 2i + 1) by position * inv_freq[i];
+//               queries to [tokens, heads, 2, dim], keys and values to the token's row.
+//   attention:  a warp per (token, head): 32 keys at a time, a lane scores one key for both maps, then every lane sums its own
+//               value columns; running maximum and sum per map; scores, weights and sums in 32-bit.
+#include "common.cuh"
+
+namespace {
+
+constexpr int kWarps = 8;
+constexpr int kMaxOwned = 8;      // value columns per lane: vdim <= 256
+
+__device__ __forceinline__ float sigmoid(float z) { return 1.0f / (1.0f + expf(-z)); }
+
+// grid: tokens; a warp per map.  projected row: [heads * 2 * dim | kv_heads * 2 * dim | kv_heads * vdim | ...].
+template <typename T>
+__global__ void __launch_bounds__(kWarps * 32)
+diff_prepare_kernel(const T* __restrict__ projected, long long projected_stride, const float* __restrict__ q_weight, const float* __restrict__ k_weight,
+                    float eps, const float* __restrict__ inv_freq, int rotary, T* __restrict__ queries, T* __restrict__ rows,
+                    const int* __restrict__ positions, const int* __restrict__ token_seq, const int* __restrict__ page_rows, int page_stride,
+                    int page_tokens, int heads, int kv_heads, int dim, int vdim, int write_rows) {
+    grid_dependents_launch();
+    grid_dependency_wait();
+    const int token = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int position = positions[token];
+    const int row_width = kv_heads * (2 * dim + vdim);
+    const T* source_row = projected + static_cast<size_t>(token) * projected_stride;
+    T* row = nullptr;
+    if (write_rows) {
+        const int page = page_rows[static_cast<size_t>(token_seq[token]) * page_stride + position / page_tokens];
+        row = rows + (static_cast<size_t>(page) * page_tokens + position % page_tokens) * row_width;
+    }
+    const int q_maps = heads * 2, maps = q_maps + (write_rows ? kv_heads * 2 : 0);
+    for (int map = warp; map < maps; map += kWarps) {
+        const bool is_query = map < q_maps;
+        const T* source = source_row + static_cast<size_t>(map) * dim;      // the key maps follow the query maps in the projected row
+        T* target = is_query ? queries + (static_cast<size_t>(token) * q_maps + map) * dim : row + static_cast<size_t>(map - q_maps) * dim;
+        const float* weight = is_query ? q_weight : k_weight;
+        float squares = 0.0f;
+        for (int column = lane; column < dim; column += 32) {
+            const float value = to_float(source[column]);
+            squares += value * value;
+        }
+        const float inverse = 1.0f / sqrtf(warp_sum(squares) / static_cast<float>(dim) + eps);
+        for (int pair = lane; 2 * pair < dim; pair += 32) {
+            const int first = 2 * pair;
+            const bool second = first + 1 < dim;
+            float u = to_float(source[first]) * inverse * weight[first];
+            float w = second ? to_float(source[first + 1]) * inverse * weight[first + 1] : 0.0f;
+            if (first + 1 < rotary) {
+                float sine, cosine;
+                sincosf(static_cast<float>(position) * inv_freq[pair], &sine, &cosine);
+                const float a = u * cosine - w * sine, b = w * cosine + u * sine;
+                u = a; w = b;
+            }
+            target[first] = from_float<T>(u);
+            if (second) target[first + 1] = from_float<T>(w);
+        }
+    }
+    if (write_rows) {
+        const T* values = source_row + static_cast<size_t>(q_maps + kv_heads * 2) * dim;
+        T* target = row + static_cast<size_t>(kv_heads) * 2 * dim;
+        for (int column = threadIdx.x; column < kv_heads * vdim; column += blockDim.x) target[column] = values[column];
+    }
+}
+
+// grid: (tokens, ceil(heads / kWarps)); a warp per head.  Dynamic shared memory: kWarps * 2 * dim floats (the queries).
+template <typename T>
+__global__ void __launch_bounds__(kWarps * 32)
+diff_attention_kernel(const T* __restrict__ queries, const T* __restrict__ rows, const T* __restrict__ gate, long long gate_stride, T* __restrict__ out,
+                      const int* __restrict__ positions, const int* __restrict__ token_seq, const int* __restrict__ page_rows, int page_stride,
+                      int page_tokens, int heads, int kv_heads, int dim, int vdim, float scale, int window, float lambda, float eps, float post_scale) {
+    grid_dependents_launch();
+    grid_dependency_wait();
+    extern __shared__ float shared[];
+    const int token = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int head = blockIdx.y * kWarps + warp;
+    if (head >= heads) return;
+    float* query = shared + static_cast<size_t>(warp) * 2 * dim;
+    const T* q_source = queries + (static_cast<size_t>(token) * heads + head) * 2 * dim;
+    for (int column = lane; column < 2 * dim; column += 32) query[column] = to_float(q_source[column]);
+    __syncwarp();
+    const int position = positions[token];
+    const int* pages = page_rows + static_cast<size_t>(token_seq[token]) * page_stride;
+    const int group = head / (heads / kv_heads);
+    const int row_width = kv_heads * (2 * dim + vdim);
+    const int key_offset = group * 2 * dim, value_offset = kv_heads * 2 * dim + group * vdim;
+    const int first_key = window > 0 && position - window + 1 > 0 ? position - window + 1 : 0;
+    float top1 = -INFINITY, top2 = -INFINITY, sum1 = 0.0f, sum2 = 0.0f;
+    float acc1[kMaxOwned], acc2[kMaxOwned];
+#pragma unroll
+    for (int i = 0; i < kMaxOwned; ++i) acc1[i] = acc2[i] = 0.0f;
+    for (int base = first_key; base <= position; base += 32) {
+        const int key = base + lane;
+        const bool valid = key <= position;
+        long long row_index = 0;
+        float s1 = -INFINITY, s2 = -INFINITY;
+        if (valid) {
+            row_index = static_cast<long long>(pages[key / page_tokens]) * page_tokens + key % page_tokens;
+            const T* k = rows + row_index * row_width + key_offset;
+            float a = 0.0f, b = 0.0f;
+            for (int column = 0; column < dim; ++column) {
+                a = fmaf(query[column], to_float(k[column]), a);
+                b = fmaf(query[dim + column], to_float(k[dim + column]), b);
+            }
+            s1 = a * scale;
+            s2 = b * scale;
+        }
+        const float new1 = fmaxf(top1, warp_max(s1)), new2 = fmaxf(top2, warp_max(s2));     // finite: the block holds at least one key
+        const float p1 = valid ? expf(s1 - new1) : 0.0f, p2 = valid ? expf(s2 - new2) : 0.0f;
+        const float keep1 = expf(top1 - new1), keep2 = expf(top2 - new2);                    // exp(-inf) = 0 the first time
+        sum1 = sum1 * keep1 + warp_sum(p1);
+        sum2 = sum2 * keep2 + warp_sum(p2);
+        top1 = new1;
+        top2 = new2;
+#pragma unroll
+        for (int i = 0; i < kMaxOwned; ++i) { acc1[i] *= keep1; acc2[i] *= keep2; }
+        const int count = position - base + 1 < 32 ? position - base + 1 : 32;
+        for (int j = 0; j < count; ++j) {
+            const float w1 = __shfl_sync(0xffffffffu, p1, j), w2 = __shfl_sync(0xffffffffu, p2, j);
+            const long long index = __shfl_sync(0xffffffffu, row_index, j);
+            const T* v = rows + index * row_width + value_offset;
+#pragma unroll
+            for (int i = 0; i < kMaxOwned; ++i) {
+                const int column = lane + 32 * i;
+                if (column < vdim) {
+                    const float value = to_float(v[column]);
+                    acc1[i] = fmaf(w1, value, acc1[i]);
+                    acc2[i] = fmaf(w2, value, acc2[i]);
+                }
+            }
+        }
+    }
+    float squares = 0.0f;
+#pragma unroll
+    for (int i = 0; i < kMaxOwned; ++i) {
+        acc1[i] = acc1[i] / sum1 - lambda * (acc2[i] / sum2);
+        if (lane + 32 * i < vdim) squares += acc1[i] * acc1[i];
+    }
+    const float inverse = post_scale / sqrtf(warp_sum(squares) / static_cast<float>(vdim) + eps);
+#pragma unroll
+    for (int i = 0; i < kMaxOwned; ++i) {
+        const int column = lane + 32 * i;
+        if (column < vdim) {
+            float value = acc1[i] * inverse;
+            if (gate) value *= sigmoid(to_float(gate[static_cast<size_t>(token) * gate_stride + head * vdim + column]));
+            out[(static_cast<size_t>(token) * heads + head) * vdim + column] = from_float<T>(value);
+        }
+    }
+}
+
+}  // namespace
+
+TAU_EXPORT int tau_diff_prepare(int dtype, const void* projected, long long projected_stride, const float* q_weight, const float* k_weight, float eps,
+                                const float* inv_freq, int rotary, void* queries, void* rows, const int* positions, const int* token_seq,
+                                const int* page_rows, int page_stride, int page_tokens, int tokens, int heads, int kv_heads, int dim, int vdim,
+                                int write_rows, void* stream) {
+    if (tokens <= 0) return 0;
+    if (!projected || !q_weight || !k_weight || !queries || !positions || heads <= 0 || kv_heads <= 0 || dim <= 0 || vdim <= 0 || rotary < 0 || rotary > dim
+        || (rotary & 1) || (rotary > 0 && !inv_freq) || (write_rows && (!rows || !token_seq || !page_rows)))
+        return cudaErrorInvalidValue;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (dtype == TAU_F32)
+        tau_launch(diff_prepare_kernel<float>, dim3(tokens), dim3(kWarps * 32), 0, s, static_cast<const float*>(projected), projected_stride, q_weight, k_weight,
+                   eps, inv_freq, rotary, static_cast<float*>(queries), static_cast<float*>(rows), positions, token_seq, page_rows, page_stride, page_tokens,
+                   heads, kv_heads, dim, vdim, write_rows);
+    else if (dtype == TAU_BF16)
+        tau_launch(diff_prepare_kernel<bf16>, dim3(tokens), dim3(kWarps * 32), 0, s, static_cast<const bf16*>(projected), projected_stride, q_weight, k_weight,
+                   eps, inv_freq, rotary, static_cast<bf16*>(queries), static_cast<bf16*>(rows), positions, token_seq, page_rows, page_stride, page_tokens,
+                   heads, kv_heads, dim, vdim, write_rows);
+    else
+        return cudaErrorInvalidValue;
+    return tau_launch_status();
+}
+
+TAU_EXPORT int tau_diff_attention(int dtype, const void* queries, const void* rows, const void* gate, long long gate_stride, void* out, const int* positions,
+                                  const int* token_seq, const int* page_rows, int page_stride, int page_tokens, int tokens, int heads, int kv_heads,
+                                  int dim, int vdim, float scale, int window, float lambda, float eps, float post_scale, void* stream) {
+    if (tokens <= 0) return 0;
+    if (!queries || !rows || !out || !positions || !token_seq || !page_rows || heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0 || dim <= 0 || vdim <= 0
+        || vdim > 32 * kMaxOwned || window < 0)
+        return cudaErrorInvalidValue;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const size_t bytes = static_cast<size_t>(kWarps) * 2 * dim * sizeof(float);
+    if (bytes > 48 * 1024) return cudaErrorInvalidValue;
+    const dim3 grid(tokens, (heads + kWarps - 1) / kWarps), block(kWarps * 32);
+    if (dtype == TAU_F32)
+        tau_launch(diff_attention_kernel<float>, grid, block, bytes, s, static_cast<const float*>(queries), static_cast<const float*>(rows),
+                   static_cast<const float*>(gate), gate_stride, static_cast<float*>(out), positions, token_seq, page_rows, page_stride, page_tokens, heads,
+                   kv_heads, dim, vdim, scale, window, lambda, eps, post_scale);
+    else if (dtype == TAU_BF16)
+        tau_launch(diff_attention_kernel<bf16>, grid, block, bytes, s, static_cast<const bf16*>(queries), static_cast<const bf16*>(rows),
+                   static_cast<const bf16*>(gate), gate_stride, static_cast<bf16*>(out), positions, token_seq, page_rows, page_stride, page_tokens, heads,
+                   kv_heads, dim, vdim, scale, window, lambda, eps, post_scale);
+    else
+        return cudaErrorInvalidValue;
+    return tau_launch_status();
+}

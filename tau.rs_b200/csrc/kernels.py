@@ -84,7 +84,8 @@ _CLASS_OF = {
     "sample_gumbel": "selection", "store_words_host": "selection", "random_normal": "other",
     "stream_add_norm": "norm", "gated_group_norm": "norm", "gemm_simt_batched": "product", "linear_recurrence": "recurrence",
     "latent_prepare": "attention", "latent_attention": "attention", "latent_expand": "attention", "moe_route": "routing", "moe_gate_up": "experts", "moe_down": "experts", "gemm_tc_groups": "experts", "moe_sort": "routing", "moe_gather": "routing",
-    "moe_combine": "routing",
+    "moe_combine": "routing", "diff_prepare": "attention", "diff_attention": "attention", "causal_taps": "norm", "gated_add_norm": "norm",
+    "side_gate": "activation", "unit_add_mix": "norm", "norm_rows": "norm", "relu_squared": "activation",
 }
 _timing = None     # while timing: [last event, [(class, event after the launch), ...]]
 
@@ -839,6 +840,175 @@ def latent_attention(queries, rows, out, sinks, positions, token_seq, page_rows,
         ctypes.c_longlong(0 if scratch is None else scratch.numel()), _stream()), "latent_attention", 2 if splits > 1 else 1)
 
 
+# ---------------------------------------------------------------------------- differential attention
+DIFF_MAX_VALUE_DIM = 256
+
+
+def diff_prepare(projected, q_weight, k_weight, eps: float, inv_freq, rotary_dim: int, queries, rows, positions, token_seq, page_rows,
+                 n_heads: int, n_kv_heads: int, dim: int, vdim: int, write_rows: bool = True) -> None:
+    """`projected` [tokens, >= n_heads * 2 * dim + n_kv_heads * (2 * dim + vdim)] holds, per token, the two query maps of every head,
+    the two key maps of every key/value head and the values.  Every map is divided by its root mean square over `dim` (eps inside
+    the root), multiplied by `q_weight` or `k_weight` (float32 [dim]) and its first `rotary_dim` elements are turned pair by pair
+    (2i, 2i + 1) by `position * inv_freq[i]`.  Queries go to `queries` [tokens, n_heads, 2, dim]; with `write_rows` keys and values
+    go to the token's row of the cache pages `rows` [pages, 64, n_kv_heads * (2 * dim + vdim)] as [keys of all heads | values]."""
+    _on_device(projected, q_weight, k_weight, inv_freq, queries, rows, positions, token_seq, page_rows)
+    tokens = projected.shape[0]
+    row_width = n_kv_heads * (2 * dim + vdim)
+    _require(projected.shape[1] >= n_heads * 2 * dim + row_width and projected.stride(1) == 1, "the projection is too narrow")
+    _require(queries.shape == (tokens, n_heads, 2, dim) and queries.is_contiguous() and queries.dtype == projected.dtype, "queries must be [tokens, n_heads, 2, dim]")
+    _f32_vector(q_weight, dim, "the query norm weight")
+    _f32_vector(k_weight, dim, "the key norm weight")
+    _require(rotary_dim % 2 == 0 and 0 <= rotary_dim <= dim, "rotary_dim must be even and at most dim")
+    if rotary_dim:
+        _f32_vector(inv_freq, rotary_dim // 2, "the rotation's frequencies")
+    _int_vector(positions, "positions")
+    if write_rows:
+        _int_vector(token_seq, "token_seq")
+        _require(rows.shape[1:] == (PAGE_TOKENS, row_width) and rows.is_contiguous() and rows.dtype == projected.dtype, "cache rows must be [pages, 64, row width]")
+        _require(page_rows.dtype == torch.int32 and page_rows.dim() == 2 and page_rows.is_contiguous(), "page rows must be int32 [sequences, stride]")
+    library = build.load_library("diff_attention.cu")
+    _check(library.tau_diff_prepare(
+        _code(projected), _pointer(projected), ctypes.c_longlong(projected.stride(0)), _pointer(q_weight), _pointer(k_weight), ctypes.c_float(eps),
+        _pointer(inv_freq), ctypes.c_int(rotary_dim), _pointer(queries), _pointer(rows if write_rows else None), _pointer(positions), _pointer(token_seq),
+        _pointer(page_rows), ctypes.c_int(page_rows.shape[1] if write_rows else 0), ctypes.c_int(PAGE_TOKENS), ctypes.c_int(tokens), ctypes.c_int(n_heads),
+        ctypes.c_int(n_kv_heads), ctypes.c_int(dim), ctypes.c_int(vdim), ctypes.c_int(1 if write_rows else 0), _stream()), "diff_prepare")
+
+
+def diff_attention(queries, rows, gate, out, step, page_rows, n_kv_heads: int, vdim: int, scale: float, window: int, lam: float, eps: float,
+                   post_scale: float) -> None:
+    """Two causal softmax maps per head over the cached rows of each token's sequence (within `window` positions if it is not 0):
+    `o = a1 - lam * a2`, divided by its root mean square over the head's `vdim` values (eps inside the root), times `post_scale`,
+    times `sigmoid(gate)` (`gate` [tokens, n_heads * vdim], rows any distance apart, or None); `out` [tokens, n_heads * vdim].
+    Scores, weights, sums and the norm are 32-bit."""
+    _on_device(queries, rows, gate, out, page_rows)
+    tokens, n_heads, _, dim = queries.shape
+    row_width = n_kv_heads * (2 * dim + vdim)
+    _require(queries.is_contiguous() and out.shape == (tokens, n_heads * vdim) and out.is_contiguous() and out.dtype == queries.dtype == rows.dtype,
+             "queries must be [tokens, n_heads, 2, dim] and the output [tokens, n_heads * vdim]")
+    _require(rows.shape[1:] == (PAGE_TOKENS, row_width) and rows.is_contiguous(), "cache rows must be [pages, 64, row width]")
+    _require(vdim <= DIFF_MAX_VALUE_DIM, f"values may have at most {DIFF_MAX_VALUE_DIM} elements per head")
+    if gate is not None:
+        _require(gate.shape == out.shape and gate.dtype == out.dtype and gate.stride(1) == 1, "the gate must have the output's shape and dtype")
+    _require(page_rows.dtype == torch.int32 and page_rows.dim() == 2 and page_rows.is_contiguous(), "page rows must be int32 [sequences, stride]")
+    library = build.load_library("diff_attention.cu")
+    _check(library.tau_diff_attention(
+        _code(queries), _pointer(queries), _pointer(rows), _pointer(gate), ctypes.c_longlong(0 if gate is None else gate.stride(0)), _pointer(out),
+        _pointer(step.positions), _pointer(step.token_seq), _pointer(page_rows), ctypes.c_int(page_rows.shape[1]), ctypes.c_int(PAGE_TOKENS),
+        ctypes.c_int(tokens), ctypes.c_int(n_heads), ctypes.c_int(n_kv_heads), ctypes.c_int(dim), ctypes.c_int(vdim), ctypes.c_float(scale),
+        ctypes.c_int(window), ctypes.c_float(lam), ctypes.c_float(eps), ctypes.c_float(post_scale), _stream()), "diff_attention")
+
+
+# ---------------------------------------------------------------------------- sublayer arrangement on a 32-bit stream
+def causal_taps(stream, weight, state, step, read_out, plain_out=None, update: bool = True) -> None:
+    """`read_out[t] = stream[t] + sum_j weight[:, j] * stream[t - taps + 1 + j]` over each sequence's run of the step, the rows before
+    the run's first token taken from `state[slot]` ([slots, taps - 1, width] float32: the sequence's last inputs, zeros at its start);
+    `plain_out` (optional) receives `stream` itself in the output's dtype.  With `update` the state then becomes the last `taps - 1`
+    inputs of each sequence (a second launch)."""
+    _on_device(stream, weight, state, read_out, plain_out)
+    tokens, width = stream.shape
+    taps = 0 if weight is None else weight.shape[1]      # without a weight the outputs are the stream itself, rounded
+    _require(stream.dtype == torch.float32 and stream.is_contiguous(), "the stream must be contiguous float32")
+    if weight is not None:
+        _require(weight.dtype == torch.float32 and weight.shape == (width, taps) and weight.is_contiguous() and taps >= 1, "the taps must be float32 [width, taps]")
+    if taps > 1:
+        _require(state is not None and state.dtype == torch.float32 and state.shape[1:] == (taps - 1, width) and state.is_contiguous(),
+                 "the state must be float32 [slots, taps - 1, width]")
+    update = update and taps > 1
+    _require(read_out.shape == stream.shape and read_out.is_contiguous(), "the output must match the stream")
+    if plain_out is not None:
+        _require(plain_out.shape == stream.shape and plain_out.is_contiguous() and plain_out.dtype == read_out.dtype, "the plain output must match the other")
+    library = build.load_library("sublayer.cu")
+    _check(library.tau_causal_taps(_code(read_out), _pointer(stream), _pointer(weight), _pointer(state), _pointer(step.token_seq), _pointer(step.cu_seqlens),
+                                   _pointer(step.seq_slot), _pointer(read_out), _pointer(plain_out), ctypes.c_int(tokens), ctypes.c_int(step.n_seqs),
+                                   ctypes.c_int(width), ctypes.c_int(taps), ctypes.c_int(1 if update else 0), _stream()), "causal_taps", 2 if update else 1)
+
+
+def gated_add_norm(source, target, branch, gate, weight, bias, eps: float, centred: bool, copy_out=None) -> None:
+    """`target = source + norm(branch * sigmoid(gate)) * weight + bias` row by row on a 32-bit stream (`target` may be `source`):
+    the norm subtracts the mean and divides by the root of the variance plus eps (`centred`, a layer norm) or divides by the root of
+    the mean square plus eps.  `gate` (rows any distance apart) and `bias` may be None.  `copy_out` receives the new rows rounded."""
+    _on_device(source, target, branch, gate, weight, bias, copy_out)
+    rows, width = source.shape
+    _require(source.dtype == target.dtype == torch.float32 and source.is_contiguous() and target.is_contiguous() and target.shape == source.shape,
+             "source and target must be contiguous float32 of one shape")
+    _require(branch.shape == source.shape and branch.is_contiguous(), "the branch must match the stream")
+    if gate is not None:
+        _require(gate.shape == source.shape and gate.stride(1) == 1, "the gate must match the stream")
+    _f32_vector(weight, width, "the norm weight")
+    _f32_vector(bias, width, "the norm bias")
+    if copy_out is not None:
+        _require(copy_out.shape == source.shape and copy_out.is_contiguous(), "the copy must match the stream")
+    library = build.load_library("sublayer.cu")
+    _check(library.tau_gated_add_norm(_code(copy_out) if copy_out is not None else 0, _pointer(source), _pointer(target), _pointer(branch), ctypes.c_int(_code(branch)),
+                                      _pointer(gate), ctypes.c_int(_code(gate) if gate is not None else 0), ctypes.c_longlong(0 if gate is None else gate.stride(0)),
+                                      _pointer(weight), _pointer(bias), _pointer(copy_out), ctypes.c_int(rows), ctypes.c_int(width), ctypes.c_float(eps),
+                                      ctypes.c_int(1 if centred else 0), _stream()), "gated_add_norm")
+
+
+def side_gate(z, table, token_ids, offset: int, out) -> None:
+    """`out[t, c] = gelu_tanh(z[t, c]) * table[token_ids[t], offset + c]`, the tanh form of GELU in 32-bit."""
+    _on_device(z, table, token_ids, out)
+    rows, dim = z.shape
+    _require(z.is_contiguous() and out.is_contiguous() and out.shape == z.shape and out.dtype == z.dtype == table.dtype and table.is_contiguous(),
+             "z, the table and the output must be contiguous and of one dtype")
+    _require(0 <= offset and offset + dim <= table.shape[1], "the table has no such columns")
+    _int_vector(token_ids, "token ids")
+    library = build.load_library("sublayer.cu")
+    _check(library.tau_side_gate(_code(z), _pointer(z), _pointer(table), _pointer(token_ids), _pointer(out), ctypes.c_int(rows), ctypes.c_int(dim),
+                                 ctypes.c_int(table.shape[1]), ctypes.c_int(offset), ctypes.c_int(table.shape[0]), _stream()), "side_gate")
+
+
+def unit_add_mix(source, y, weight, eps: float, result, results=None, mix=None, out=None, copy_out=None) -> None:
+    """`result = source + y / sqrt(mean(y^2) + eps) * weight` row by row on a 32-bit stream (`result = source` if `y` is None).  With `mix` (float32 [count]) and
+    `results` ([count - 1 or more, rows, width] float32: the earlier results, `result` being the newest) `out = sum_j mix[j] * results[j]`
+    with `results[count - 1]` standing for `result`.  `copy_out` receives `out` (or `result`, without `mix`) rounded."""
+    _on_device(source, y, weight, result, results, mix, out, copy_out)
+    rows, width = source.shape
+    _require(source.dtype == result.dtype == torch.float32 and source.is_contiguous() and result.is_contiguous() and result.shape == source.shape,
+             "source and result must be contiguous float32 of one shape")
+    if y is not None:
+        _require(y.shape == source.shape and y.is_contiguous() and weight is not None, "y must match the stream and have a weight")
+    _f32_vector(weight, width, "the norm weight")
+    count = 0
+    if mix is not None:
+        count = mix.numel()
+        _require(mix.dtype == torch.float32 and mix.is_contiguous() and count >= 1, "the mix must be a float32 vector")
+        _require(out is not None and out.dtype == torch.float32 and out.shape == source.shape and out.is_contiguous(), "the mixed output must match the stream")
+        if count > 1:
+            _require(results is not None and results.dtype == torch.float32 and results.shape[0] >= count - 1 and results.shape[1:] == source.shape
+                     and results.is_contiguous(), "results must be float32 [count - 1 or more, rows, width]")
+    if copy_out is not None:
+        _require(copy_out.shape == source.shape and copy_out.is_contiguous(), "the copy must match the stream")
+    library = build.load_library("sublayer.cu")
+    _check(library.tau_unit_add_mix(_code(copy_out) if copy_out is not None else 0, _pointer(source), _pointer(y), ctypes.c_int(_code(y) if y is not None else 0), _pointer(weight),
+                                    _pointer(result), _pointer(results), ctypes.c_longlong(rows * width), _pointer(mix), ctypes.c_int(count), _pointer(out),
+                                    _pointer(copy_out), ctypes.c_int(rows), ctypes.c_int(width), ctypes.c_float(eps), _stream()), "unit_add_mix")
+
+
+def norm_rows(values, rows, weight, bias, eps: float, centred: bool, out) -> None:
+    """`out[i] = norm(values[rows[i]]) * weight + bias` (`rows` None: every row): a layer norm (`centred`) or an RMS norm, in 32-bit."""
+    _on_device(values, rows, weight, bias, out)
+    width = values.shape[-1]
+    _require(values.is_contiguous() and out.is_contiguous() and out.shape[-1] == width, "input and output must be contiguous and as wide")
+    _f32_vector(weight, width, "the norm weight")
+    _f32_vector(bias, width, "the norm bias")
+    if rows is not None:
+        _int_vector(rows, "row numbers")
+    count = out.numel() // width
+    _require(count == (rows.shape[0] if rows is not None else values.numel() // width), "output row count does not match")
+    library = build.load_library("sublayer.cu")
+    _check(library.tau_norm_rows(_code(out), _pointer(values), ctypes.c_int(_code(values)), _pointer(rows), _pointer(weight), _pointer(bias), _pointer(out),
+                                 ctypes.c_int(count), ctypes.c_int(width), ctypes.c_float(eps), ctypes.c_int(1 if centred else 0), _stream()), "norm_rows")
+
+
+def relu_squared(z, out) -> None:
+    """`out = max(z, 0)^2`."""
+    _on_device(z, out)
+    _require(z.is_contiguous() and out.is_contiguous() and z.shape == out.shape and z.dtype == out.dtype, "input and output must match")
+    library = build.load_library("sublayer.cu")
+    _check(library.tau_relu_squared(_code(z), _pointer(z), _pointer(out), ctypes.c_longlong(z.numel()), _stream()), "relu_squared")
+
+
 # ---------------------------------------------------------------------------- linear recurrences
 RECURRENCE_MAX_KEY_DIM = 512
 
@@ -882,14 +1052,15 @@ def linear_recurrence(q, k, v, gates, decays, state, cu_seqlens, seq_slot, out, 
 
 # ---------------------------------------------------------------------------- routed experts
 def moe_route(hidden, router, correction, shared_gate_weight, chosen, weights, shared_gate, top: int, softmax: bool = False,
-              renormalize: bool = False) -> None:
+              renormalize: bool = False, logit_bias=None) -> None:
     """Scores the experts of every token in 32-bit and chooses `top` of them: `router` float32 [experts, width];
-    scores = sigmoid (or softmax) of `router @ hidden`; chosen by score + `correction` (float32 [experts] or None), the
+    scores = sigmoid (or softmax) of `router @ hidden + logit_bias` (float32 [experts] or None); chosen by score + `correction` (float32 [experts] or None), the
     lowest index among equals; `weights` are the chosen scores themselves (divided by their sum with `renormalize`).
     `shared_gate[token] = sigmoid(shared_gate_weight . hidden[token])` where that weight (float32 [width]) is given."""
-    _on_device(hidden, router, correction, shared_gate_weight, chosen, weights, shared_gate)
+    _on_device(hidden, router, correction, shared_gate_weight, chosen, weights, shared_gate, logit_bias)
     tokens, width = hidden.shape
     experts = router.shape[0]
+    _f32_vector(logit_bias, experts, "the router's bias")
     _require(hidden.is_contiguous() and router.dtype == torch.float32 and router.shape == (experts, width) and router.is_contiguous(),
              "the router must be float32 [experts, width]")
     _f32_vector(correction, experts, "the correction")
@@ -899,7 +1070,7 @@ def moe_route(hidden, router, correction, shared_gate_weight, chosen, weights, s
     if shared_gate_weight is not None:
         _require(shared_gate is not None and shared_gate.dtype == torch.float32 and shared_gate.numel() == tokens, "one shared gate per token")
     library = build.load_library("moe.cu")
-    _check(library.tau_moe_route(_code(hidden), _pointer(hidden), _pointer(router), _pointer(correction), _pointer(shared_gate_weight),
+    _check(library.tau_moe_route(_code(hidden), _pointer(hidden), _pointer(router), _pointer(logit_bias), _pointer(correction), _pointer(shared_gate_weight),
                                  _pointer(chosen), _pointer(weights), _pointer(shared_gate), ctypes.c_int(tokens), ctypes.c_int(width),
                                  ctypes.c_int(experts), ctypes.c_int(top), ctypes.c_int(1 if softmax else 0), ctypes.c_int(1 if renormalize else 0),
                                  _stream()), "moe_route")

@@ -16,6 +16,8 @@ def all_libraries() -> List[Tuple[str, Sequence[str]]]:
         ("stream32.cu", ()),
         ("latent_attention.cu", ()),
         ("moe.cu", ()),
+        ("sublayer.cu", ()),
+        ("diff_attention.cu", ()),
         *[("recurrence.cu", (f"TAU_KEY_DIM={key_dim}",)) for key_dim in (16, 32, 64, 128)],
         # Specialised libraries: the head sizes of the benchmark shape and of the tests' tiny models.
         *[("attention_decode.cu", (f"TAU_HEAD_DIM={head_dim}", f"TAU_DTYPE={dtype}"))

@@ -1,7 +1,7 @@
 // Routed experts, token by token: a router that scores the experts in 32-bit and picks `top` of them, the chosen
 // experts' gated products, and the weighted sum of their outputs (plus a shared expert's, scaled by its own gate).
 //
-//   route:    z = W_router h (32-bit weights and sums); s = sigmoid(z) or softmax(z); the `top` largest of
+//   route:    z = W_router h + bias (32-bit weights and sums; the bias is optional); s = sigmoid(z) or softmax(z); the `top` largest of
 //             s + correction are chosen (the lowest index among equals), their weights are s itself, divided by
 //             their sum if `renormalize`; shared_gate = sigmoid(w_sg . h).
 //   gate_up:  inner[token, place] = silu(W_gate[e] h) * (W_up[e] h) for the expert e of each (token, place).
@@ -124,7 +124,7 @@ __device__ __forceinline__ void warp_dot_pair<bf16>(const bf16* __restrict__ fir
 
 template <typename T>
 __global__ void __launch_bounds__(kThreads)
-moe_route_kernel(const T* __restrict__ hidden, const float* __restrict__ router, const float* __restrict__ correction,
+moe_route_kernel(const T* __restrict__ hidden, const float* __restrict__ router, const float* __restrict__ logit_bias, const float* __restrict__ correction,
                  const float* __restrict__ shared_gate_weight, int* __restrict__ chosen, float* __restrict__ weights, float* __restrict__ shared_gate,
                  int width, int experts, int top, int softmax, int renormalize) {
     grid_dependents_launch();
@@ -138,7 +138,7 @@ moe_route_kernel(const T* __restrict__ hidden, const float* __restrict__ router,
     __syncthreads();
     for (int expert = warp; expert < experts; expert += kWarps) {
         const float z = warp_dot(router + static_cast<size_t>(expert) * width, row, width, lane);
-        if (lane == 0) scores[expert] = z;
+        if (lane == 0) scores[expert] = z + (logit_bias ? logit_bias[expert] : 0.0f);
     }
     if (shared_gate_weight && warp == kWarps - 1) {
         const float z = warp_dot(shared_gate_weight, row, width, lane);
@@ -306,8 +306,8 @@ int launch_all(int what, const void* a, const void* b, const void* c, const void
         const size_t bytes = (static_cast<size_t>(width) + 2 * experts) * sizeof(float);
         if (bytes > 48 * 1024 && cudaFuncSetAttribute(moe_route_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes)) != cudaSuccess)
             return cudaErrorInvalidValue;
-        tau_launch(moe_route_kernel<T>, dim3(tokens), dim3(kThreads), bytes, s, static_cast<const T*>(a), static_cast<const float*>(b), static_cast<const float*>(c),
-                   static_cast<const float*>(d), static_cast<int*>(o1), static_cast<float*>(o2), static_cast<float*>(o3), width, experts, top, flag_a, flag_b);
+        tau_launch(moe_route_kernel<T>, dim3(tokens), dim3(kThreads), bytes, s, static_cast<const T*>(a), static_cast<const float*>(b), static_cast<const float*>(e),
+                   static_cast<const float*>(c), static_cast<const float*>(d), static_cast<int*>(o1), static_cast<float*>(o2), static_cast<float*>(o3), width, experts, top, flag_a, flag_b);
     } else if (what == 1) {
         const int per_block = 64;
         const size_t bytes = static_cast<size_t>(width) * sizeof(float);
@@ -329,14 +329,14 @@ int launch_all(int what, const void* a, const void* b, const void* c, const void
 
 }  // namespace
 
-TAU_EXPORT int tau_moe_route(int dtype, const void* hidden, const float* router, const float* correction, const float* shared_gate_weight, int* chosen,
+TAU_EXPORT int tau_moe_route(int dtype, const void* hidden, const float* router, const float* logit_bias, const float* correction, const float* shared_gate_weight, int* chosen,
                              float* weights, float* shared_gate, int tokens, int width, int experts, int top, int softmax, int renormalize, void* stream) {
     if (tokens <= 0) return 0;
     if (!hidden || !router || !chosen || !weights || width <= 0 || experts <= 0 || top <= 0 || top > experts || (shared_gate_weight && !shared_gate))
         return cudaErrorInvalidValue;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (dtype == TAU_F32) return launch_all<float>(0, hidden, router, correction, shared_gate_weight, nullptr, nullptr, chosen, weights, shared_gate, tokens, width, 0, experts, top, softmax, renormalize, s);
-    if (dtype == TAU_BF16) return launch_all<bf16>(0, hidden, router, correction, shared_gate_weight, nullptr, nullptr, chosen, weights, shared_gate, tokens, width, 0, experts, top, softmax, renormalize, s);
+    if (dtype == TAU_F32) return launch_all<float>(0, hidden, router, correction, shared_gate_weight, logit_bias, nullptr, chosen, weights, shared_gate, tokens, width, 0, experts, top, softmax, renormalize, s);
+    if (dtype == TAU_BF16) return launch_all<bf16>(0, hidden, router, correction, shared_gate_weight, logit_bias, nullptr, chosen, weights, shared_gate, tokens, width, 0, experts, top, softmax, renormalize, s);
     return cudaErrorInvalidValue;
 }
 

@@ -77,6 +77,8 @@ class StepContext:
     all_single: bool             # every sequence brings exactly one token
     decode_splits: int = 0       # context splits of decode attention, fixed by a captured graph (0: chosen per step)
     all_fresh: bool = False      # every sequence starts at position 0 in this step (nothing of it is cached yet)
+    results: object = None       # [runs + 1, n_tokens, hidden] 32-bit, where the model keeps every run's result (`ModelSpec.keeps_results`)
+    run: int = 0                 # index of the schedule entry that is being computed
 
 
 def fill_step(layout: StepLayout, out: np.ndarray, entries: Sequence[StepEntry], starts: Sequence[int], cache) -> None:

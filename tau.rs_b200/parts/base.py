@@ -126,5 +126,18 @@ class Block(Part):
         """The mixer's answer (see `Mixer.decode_blocks`)."""
         return None
 
+    def extra_cache_needs(self) -> Dict[str, CacheNeed]:
+        """What the block keeps for a sequence beside its mixer's cache, by role (the tail of inputs of a convolution, say).  The
+        schedule entry names a cache group and layer for each role (`ScheduleEntry.extra_cache`); `forward` finds the views under
+        `cache.extra[role]`."""
+        return {}
+
+    def shared_tensor_names(self) -> Tuple[str, ...]:
+        """Names among `ModelSpec.shared_tensors` that the block reads; the model hands each over through `bind_shared`."""
+        return ()
+
+    def bind_shared(self, name: str, tensor) -> None:
+        raise KeyError(name)
+
     def forward(self, residual, branch, step, cache, writes_cache: bool):
         raise NotImplementedError

@@ -8,6 +8,11 @@ Weight names: `<prefix>.input_layernorm`, `<prefix>.self_attn`,
 """
 from __future__ import annotations
 
+import math
+
+import torch
+
+from ..csrc import kernels
 from .base import Block
 from .registry import build, register_block
 
@@ -105,3 +110,158 @@ class ParallelBlock(Block):
         if self.feed_forward is None:
             return residual, mixed
         return residual, (mixed, self.feed_forward.forward(normalized, step))
+
+
+@register_block("sublayer_norm")
+class SublayerNormBlock(Block):
+    """Norms on what the sublayers return, on a 32-bit residual stream `x`:
+
+        read = x + conv(x)                          (a causal convolution over time per channel, if `input_taps`; else read = x)
+        x <- x + norm1(sigmoid(W_g1 x + b_g1) * mixer(read))
+        x <- x + norm2(sigmoid(W_g2 x + b_g2) * feed_forward(x))        (if there is a feed-forward)
+        y = W_proj (gelu_tanh(W_gate x) * e[token]);  x <- x + y / rms(y) * w_side      (if `token_side`)
+        X_(run + 1) = x;  handed on: sum_j mix[j] * X_j over the first `depth_mix` results     (if `depth_mix`)
+
+    Each `x <- x + norm(...)` is one kernel that also rounds the new `x` for the products that read it next.  The convolution's
+    last `input_taps - 1` inputs are state of the sequence (`extra_cache_needs()["taps"]`, 32-bit).  Weight names under the
+    prefix: `norm1`, `norm2` (and their biases), `mix.*`, `mlp.*`, `canon1` [width, taps], `rg1`, `rg2` (with `.b`), `dwa`
+    [depth_mix], `side.gate`, `side.proj`, `side.norm`.
+    """
+
+    mixer_name = "mix"
+    feed_forward_name = "mlp"
+    mixer_norm_name = "norm1"
+    feed_forward_norm_name = "norm2"
+    taps_name = "canon1"
+    mixer_gate_name = "rg1"
+    feed_forward_gate_name = "rg2"
+    mix_name = "dwa"
+    side_name = "side"
+
+    def __init__(self, spec, dtype, device):
+        from ..weights.tensor_spec import TensorSpec
+        from .linear import StackedLinear
+
+        self.spec, self.dtype = spec, dtype
+        prefix, width = spec.prefix, spec.mixer_norm.width
+        self.width = width
+        self.mixer_norm = build("norm", spec.mixer_norm, name=f"{prefix}.{self.mixer_norm_name}", dtype=dtype, device=device)
+        self.mixer = build("mixer", spec.mixer, prefix=f"{prefix}.{self.mixer_name}", dtype=dtype, device=device)
+        self.feed_forward = self.feed_forward_norm = self.mixer_gate = self.feed_forward_gate = self.side_gate = self.side_proj = None
+        if spec.feed_forward is not None:
+            self.feed_forward = build("feed_forward", spec.feed_forward, prefix=f"{prefix}.{self.feed_forward_name}", dtype=dtype, device=device)
+            self.feed_forward_norm = build("norm", spec.feed_forward_norm, name=f"{prefix}.{self.feed_forward_norm_name}", dtype=dtype, device=device)
+        for norm in (spec.mixer_norm, spec.feed_forward_norm if spec.feed_forward is not None else None):
+            if norm is not None and norm.kind not in ("layer_norm", "rms_norm"):
+                raise ValueError(f"the block's kernel computes layer_norm and rms_norm; a norm of kind {norm.kind!r} is not served")
+        names = dict(weight_suffix="", bias_suffix=".b")
+        if spec.residual_gate:
+            self.mixer_gate = StackedLinear([(f"{prefix}.{self.mixer_gate_name}", width)], width, True, dtype, device, **names)
+            if self.feed_forward is not None:
+                self.feed_forward_gate = StackedLinear([(f"{prefix}.{self.feed_forward_gate_name}", width)], width, True, dtype, device, **names)
+        self._own = {}
+        if spec.input_taps:
+            self._own[f"{prefix}.{self.taps_name}"] = TensorSpec((width, spec.input_taps), role="vector", std=0.1)
+        if spec.depth_mix:
+            self._own[f"{prefix}.{self.mix_name}"] = TensorSpec((spec.depth_mix,), role="vector", std=0.5)
+        side = spec.token_side
+        if side is not None:
+            self.side_gate = StackedLinear([(f"{prefix}.{self.side_name}.gate", side.dim)], width, False, dtype, device, **names)
+            self.side_proj = StackedLinear([(f"{prefix}.{self.side_name}.proj", width)], side.dim, False, dtype, device, **names)
+            self._own[f"{prefix}.{self.side_name}.norm"] = TensorSpec((width,), role="vector", init="ones")
+        self._held = {}
+        self.taps = self.mix = self.side_norm = self.side_table = None
+        self._children = tuple(part for part in (self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward, self.mixer_gate,
+                                                 self.feed_forward_gate, self.side_gate, self.side_proj) if part is not None)
+        self.capturable = all(getattr(part, "capturable", True) for part in self._children)
+
+    cache_need = PreNormBlock.cache_need
+    decode_blocks = PreNormBlock.decode_blocks
+
+    def extra_cache_needs(self):
+        from .base import CacheNeed
+
+        if self.spec.input_taps > 1:
+            return {"taps": CacheNeed("state", state_shape=(self.spec.input_taps - 1, self.width))}
+        return {}
+
+    def shared_tensor_names(self):
+        return () if self.spec.token_side is None else (self.spec.token_side.table,)
+
+    def bind_shared(self, name, tensor):
+        if self.spec.token_side is None or name != self.spec.token_side.table:
+            raise KeyError(name)
+        self.side_table = tensor
+
+    def tensor_specs(self):
+        specs = dict(self._own)
+        for part in self._children:
+            specs.update(part.tensor_specs())
+        return specs
+
+    def assign(self, name, tensor):
+        if name in self._own:
+            self._held[name] = tensor
+            return
+        for part in self._children:
+            if name in part.tensor_specs():
+                return part.assign(name, tensor)
+        raise KeyError(name)
+
+    def finalize_weights(self):
+        prefix, spec = self.spec.prefix, self.spec
+        for part in self._children:
+            part.finalize_weights()
+        self.taps = self._held.pop(f"{prefix}.{self.taps_name}") if spec.input_taps else None
+        self.mix = self._held.pop(f"{prefix}.{self.mix_name}") if spec.depth_mix else None
+        self.side_norm = self._held.pop(f"{prefix}.{self.side_name}.norm") if spec.token_side is not None else None
+
+    def bytes_read_per_step(self, dtype) -> int:
+        own = sum(4 * math.prod(spec.shape) for spec in self._own.values())
+        return own + sum(part.bytes_read_per_step(dtype) for part in self._children)
+
+    def _join(self, source, target, result, gate, norm, spec_norm, copy):
+        kernels.gated_add_norm(source, target, result, gate, norm.weight, getattr(norm, "bias", None), spec_norm.eps, spec_norm.kind == "layer_norm", copy)
+
+    def forward(self, residual, branch, step, cache, writes_cache: bool):
+        spec = self.spec
+        if branch is not None:
+            raise ValueError("this block reads a finished stream; the block before it must not leave a branch pending")
+        if residual.dtype != torch.float32:
+            raise ValueError("this block keeps its residual stream in 32-bit (ModelSpec.residual_dtype)")
+        x, shape, device = residual, residual.shape, residual.device
+        # What the products read: the stream rounded once (`plain`), and for the mixer the stream plus its convolution (`read`).
+        read = torch.empty(shape, dtype=self.dtype, device=device)
+        plain = torch.empty(shape, dtype=self.dtype, device=device) if (spec.input_taps and spec.residual_gate) else None
+        state = cache.extra["taps"].state if spec.input_taps > 1 else None
+        kernels.causal_taps(x, self.taps, state, step, read, plain, update=writes_cache)
+        mixed = self.mixer.forward(read, step, cache, writes_cache)
+        gate = None if self.mixer_gate is None else self.mixer_gate.forward(read if plain is None else plain)
+        if spec.depth_mix:
+            if step.results is None or spec.depth_mix != step.run + 2:
+                raise ValueError("the block mixes the model's results: the model must keep them, and this run must be number depth_mix - 2")
+            target = step.results[step.run + 1]
+        else:
+            target = x
+        rounded = torch.empty(shape, dtype=self.dtype, device=device)
+        self._join(x, target, mixed, gate, self.mixer_norm, spec.mixer_norm, rounded)
+        x = target
+        if self.feed_forward is not None:
+            fed = self.feed_forward.forward(rounded, step)
+            gate = None if self.feed_forward_gate is None else self.feed_forward_gate.forward(rounded)
+            after = torch.empty(shape, dtype=self.dtype, device=device)
+            self._join(x, x, fed, gate, self.feed_forward_norm, spec.feed_forward_norm, after)
+            rounded = after
+        y = None
+        if spec.token_side is not None:
+            side = spec.token_side
+            pre = self.side_gate.forward(rounded)
+            kernels.side_gate(pre, self.side_table, step.token_ids, side.offset, pre)
+            y = self.side_proj.forward(pre, out_dtype=torch.float32)
+        if not spec.depth_mix:
+            if y is not None:
+                kernels.unit_add_mix(x, y, self.side_norm, spec.token_side.eps, x)
+            return x, None
+        out = torch.empty(shape, dtype=torch.float32, device=device)
+        kernels.unit_add_mix(x, y, self.side_norm, 0.0 if y is None else spec.token_side.eps, x, step.results, self.mix, out)
+        return out, None

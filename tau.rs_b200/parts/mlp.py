@@ -48,3 +48,32 @@ class SwiGLU(FeedForward):
         activated = torch.empty((hidden.shape[0], self.spec.intermediate), dtype=hidden.dtype, device=hidden.device)
         kernels.silu_mul(stacked, activated)
         return self.down.forward(activated)
+
+
+@register_feed_forward("dense_mlp")
+class DenseFeedForward(FeedForward):
+    """`down(act(up(x) + b_up)) + b_down`; the biases ride with the products, the activation is one kernel; the result is 32-bit."""
+
+    def __init__(self, spec, prefix: str, dtype, device):
+        if spec.activation != "relu_squared":
+            raise ValueError(f"unknown activation {spec.activation!r}")
+        self.spec = spec
+        names = dict(weight_suffix=spec.weight_suffix, bias_suffix=spec.bias_suffix)
+        self.up = StackedLinear([(f"{prefix}.{spec.up_name}", spec.intermediate)], spec.hidden, spec.bias, dtype, device, **names)
+        self.down = StackedLinear([(f"{prefix}.{spec.down_name}", spec.hidden)], spec.intermediate, spec.bias, dtype, device, **names)
+
+    def tensor_specs(self):
+        return {**self.up.tensor_specs(), **self.down.tensor_specs()}
+
+    def assign(self, name, tensor):
+        part = self.up if name in self.up.tensor_specs() else self.down
+        part.assign(name, tensor)
+
+    def finalize_weights(self):
+        self.up.finalize_weights()
+        self.down.finalize_weights()
+
+    def forward(self, hidden, step):
+        inner = self.up.forward(hidden)
+        kernels.relu_squared(inner, inner)
+        return self.down.forward(inner, out_dtype=torch.float32)

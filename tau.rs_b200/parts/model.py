@@ -38,6 +38,11 @@ class DecoderModel:
             if not 0 <= entry.layer < len(self.blocks):
                 raise ValueError(f"schedule names layer {entry.layer}, the model has {len(self.blocks)}")
         self._groups = self._collect_cache_groups()
+        self._shared = {name: TensorSpec(tuple(shape), role=role) for name, shape, role in getattr(spec, "shared_tensors", ())}
+        self.shared: Dict[str, torch.Tensor] = {}
+        for name in self._shared:
+            if name in self._owner:
+                raise ValueError(f"the shared tensor {name} is also a part's own")
 
     # ---- cache needs -------------------------------------------------------------
     def _collect_cache_groups(self) -> Dict[str, Tuple[CacheNeed, int]]:
@@ -59,6 +64,18 @@ class DecoderModel:
                 written.add(key)
             elif key not in written:
                 raise ValueError(f"schedule entry for layer {entry.layer} reads cache {key} before any entry writes it")
+        # What blocks keep beside their mixers' caches: a group and a cache layer for every role that a block names.
+        for entry in self.spec.schedule:
+            needs = self.blocks[entry.layer].extra_cache_needs()
+            named = {role: (group, layer) for role, group, layer in getattr(entry, "extra_cache", ())}
+            if set(named) != set(needs):
+                raise ValueError(f"layer {entry.layer} keeps {sorted(needs)} beside its mixer's cache; its schedule entry names {sorted(named)}")
+            for role, need in needs.items():
+                group, layer = named[role]
+                known = groups.get(group)
+                if known is not None and known[0] != need:
+                    raise ValueError(f"cache group {group!r} is shared by layers with different needs")
+                groups[group] = (need, max(known[1] if known else 0, layer + 1))
         return groups
 
     def cache_groups(self) -> Dict[str, Tuple[CacheNeed, int]]:
@@ -71,6 +88,7 @@ class DecoderModel:
         specs = {spec.embedding_name: TensorSpec((spec.vocab_size, spec.hidden), role="matrix")}
         for part in self._parts:
             specs.update(part.tensor_specs())
+        specs.update(self._shared)
         if not spec.tie_head:
             specs[spec.head_name] = TensorSpec((spec.vocab_size, spec.hidden), role="matrix", fallback=spec.embedding_name)
         return specs
@@ -88,10 +106,15 @@ class DecoderModel:
             self.embedding = tensor
         elif name == self.spec.head_name and not self.spec.tie_head:
             self.head = tensor
+        elif name in self._shared:
+            self.shared[name] = tensor
         else:
             self._owner[name].assign(name, tensor)
 
     def finalize_weights(self) -> None:
+        for block in self.blocks:
+            for name in block.shared_tensor_names():
+                block.bind_shared(name, self.shared[name])
         for part in self._parts:
             part.finalize_weights()
         if self.spec.tie_head:
@@ -115,14 +138,25 @@ class DecoderModel:
     def forward(self, step, cache) -> Optional[torch.Tensor]:
         """Runs the step's tokens; returns 32-bit logits `[wanted, vocab]`, or None if nothing is wanted."""
         spec = self.spec
-        residual = torch.empty((step.n_tokens, spec.hidden), dtype=self.residual_dtype, device=self.device)
+        if getattr(spec, "keeps_results", False):      # the embedding output and every run's result stay until the step ends
+            step.results = torch.empty((len(spec.schedule) + 1, step.n_tokens, spec.hidden), dtype=self.residual_dtype, device=self.device)
+            residual = step.results[0]
+        else:
+            residual = torch.empty((step.n_tokens, spec.hidden), dtype=self.residual_dtype, device=self.device)
         kernels.embedding(step.token_ids, self.embedding, residual)
         if self.input_position is not None:
             self.input_position.add_to(residual, step)
         branch = None
-        for entry in spec.schedule:
+        for run, entry in enumerate(spec.schedule):
             view = None if entry.cache_group is None else cache.layer_view(entry.cache_group, entry.cache_layer)
+            extra = getattr(entry, "extra_cache", ())
+            if extra:
+                if view is None:
+                    raise ValueError("a block that keeps something beside its mixer's cache needs that cache as well")
+                view.extra = {role: cache.layer_view(group, layer) for role, group, layer in extra}
+            step.run = run
             residual, branch = self.blocks[entry.layer].forward(residual, branch, step, view, entry.writes_cache)
+        step.results = None
         if step.n_wanted == 0:
             return None
         normalized = self.final_norm.forward(residual, rows=step.want_rows, branch=branch)

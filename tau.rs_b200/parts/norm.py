@@ -40,3 +40,34 @@ class RMSNorm(Norm):
         out = torch.empty(residual.shape, dtype=self.dtype or residual.dtype, device=residual.device)
         kernels.add_rms_norm(branch, residual, self.weight, self.spec.eps, out)
         return out
+
+
+@register_norm("layer_norm")
+class LayerNorm(Norm):
+    """`(x - mean) / sqrt(variance + eps) * w + b`, the variance being the mean of the squared deviations; statistics in 32-bit,
+    one rounding.  The bias is the tensor `<name><spec.bias_suffix>`.  The input may be a residual stream kept in 32-bit."""
+
+    def __init__(self, spec, name: str, dtype, device):
+        self.spec, self.name, self.bias_name = spec, name, name + spec.bias_suffix
+        self.dtype = dtype
+        self.weight = self.bias = None
+
+    def tensor_specs(self):
+        width = self.spec.width
+        return {self.name: TensorSpec((width,), role="vector", init="ones"), self.bias_name: TensorSpec((width,), role="vector")}
+
+    def assign(self, name, tensor):
+        if name == self.name:
+            self.weight = tensor
+        elif name == self.bias_name:
+            self.bias = tensor
+        else:
+            raise KeyError(name)
+
+    def forward(self, values, rows=None, branch=None):
+        if branch is not None:
+            raise ValueError("a layer norm of this kind reads finished rows; a pending branch must be added first")
+        count = values.shape[0] if rows is None else rows.shape[0]
+        out = torch.empty((count, self.spec.width), dtype=self.dtype or values.dtype, device=values.device)
+        kernels.norm_rows(values, rows, self.weight, self.bias, self.spec.eps, True, out)
+        return out

@@ -1,6 +1,6 @@
 """Routed experts: each token passes `top` of `experts` gated feed-forwards, and optionally a shared one.
 
-    z = W_router h (32-bit);   s = sigmoid(z) (or softmax(z))
+    z = W_router h (+ b_router) (32-bit);   s = sigmoid(z) (or softmax(z))
     chosen = the `top` experts with the largest s + correction;   weights = s of the chosen (renormalised only if asked)
     out = sum over chosen e of weight_e * W_down,e (silu(W_gate,e h) * (W_up,e h))  +  sigmoid(w_sg . h) * shared(h)
 
@@ -16,7 +16,7 @@ The router, the choice and the weighted sum are 32-bit, and so is the output.  T
 
 Both compute the same sums in 32-bit from the same roundings of the inputs; they differ as two product kernels differ.
 A step reads only the experts that its tokens chose, which `bytes_read_per_step` accounts for.  Tensor names under the
-prefix: `router`, `correction`, `e<j>.gate`, `e<j>.up`, `e<j>.down`, `shared.gate|up|down`, `shared.sg`.
+prefix: `router`, `router.b`, `correction`, `e<j>.gate`, `e<j>.up`, `e<j>.down`, `shared.gate|up|down`, `shared.sg`.
 """
 from __future__ import annotations
 
@@ -45,6 +45,8 @@ class RoutedExperts(FeedForward):
         self._own = {f"{prefix}.router": TensorSpec((spec.experts, spec.hidden), role="vector")}
         if spec.correction:
             self._own[f"{prefix}.correction"] = TensorSpec((spec.experts,), role="vector")
+        if getattr(spec, "router_bias", False):
+            self._own[f"{prefix}.router.b"] = TensorSpec((spec.experts,), role="vector")
         if spec.shared_gate:
             self._own[f"{prefix}.shared.sg"] = TensorSpec((1, spec.hidden), role="vector")
         for expert in range(spec.experts):
@@ -54,7 +56,7 @@ class RoutedExperts(FeedForward):
         # Where the gated product exists the experts' gate and up rows are interleaved for it (as a dense feed-forward's are).
         self.interleave = kernels.GATE_GROUP if kernels.gated_fits(spec.hidden, spec.intermediate, dtype) and spec.intermediate % 8 == 0 else 0
         self._held = {}
-        self.router = self.correction = self.shared_gate = self.gate_up = self.down = None
+        self.router = self.router_bias = self.correction = self.shared_gate = self.gate_up = self.down = None
 
     def tensor_specs(self):
         specs = dict(self._own)
@@ -76,6 +78,7 @@ class RoutedExperts(FeedForward):
             self.shared.finalize_weights()
         self.router = held.pop(f"{prefix}.router")
         self.correction = held.pop(f"{prefix}.correction") if spec.correction else None
+        self.router_bias = held.pop(f"{prefix}.router.b") if getattr(spec, "router_bias", False) else None
         self.shared_gate = held.pop(f"{prefix}.shared.sg").reshape(-1).contiguous() if spec.shared_gate else None
         group = self.interleave
 
@@ -102,7 +105,7 @@ class RoutedExperts(FeedForward):
         weights = torch.empty((tokens, spec.top), dtype=torch.float32, device=device)
         shared_gate = torch.empty((tokens,), dtype=torch.float32, device=device) if spec.shared_gate else None
         kernels.moe_route(hidden, self.router, self.correction, self.shared_gate, chosen, weights, shared_gate, spec.top,
-                          spec.score == "softmax", spec.renormalize)
+                          spec.score == "softmax", spec.renormalize, self.router_bias)
         shared_out = None if self.shared is None else self.shared.forward(hidden, step)
         out = torch.empty((tokens, spec.hidden), dtype=torch.float32, device=device)
         if self.interleave and not step.all_single and tokens * spec.top >= GROUPED_FROM and not torch.cuda.is_current_stream_capturing():
