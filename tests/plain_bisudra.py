@@ -1,4 +1,4 @@
-"""Bisudra stated plainly: one function per mechanism, float64, whole sequences, loops where a loop is clearest.
+"""Bisudra stated plainly: one function per mechanism, float64, whole sequences, masks instead of caches.
 
 Shares nothing with the library.  `weights` maps tensor names to float64 tensors, `config` is the dictionary that a
 folder's config.json holds.  Every function takes one sequence `[tokens, ...]` whose first row is position 0.
@@ -31,35 +31,32 @@ def causal_taps(h, taps_weight):
     tokens, _ = h.shape
     taps = taps_weight.shape[1]
     out = torch.zeros_like(h)
-    for t in range(tokens):
-        for j in range(taps):
-            source = t - taps + 1 + j
-            if source >= 0:
-                out[t] += taps_weight[:, j] * h[source]
+    for j in range(taps):
+        back = taps - 1 - j                      # tap j reads the row `back` positions earlier
+        if back < tokens:
+            out[back:] += taps_weight[:, j] * h[: tokens - back]
     return out
 
 
 def rotate_pairs(x, rotary_dim, base, first_position=0):
     """`x` [tokens, ..., dim]: elements (2i, 2i+1) of the first `rotary_dim` turn by `position * base^(-2i / rotary_dim)`."""
     out = x.clone()
-    for t in range(x.shape[0]):
-        for i in range(rotary_dim // 2):
-            angle = (first_position + t) * base ** (-2.0 * i / rotary_dim)
-            u, v = x[t, ..., 2 * i], x[t, ..., 2 * i + 1]
-            out[t, ..., 2 * i] = u * math.cos(angle) - v * math.sin(angle)
-            out[t, ..., 2 * i + 1] = v * math.cos(angle) + u * math.sin(angle)
+    positions = torch.arange(first_position, first_position + x.shape[0], dtype=F).view(-1, *([1] * (x.dim() - 2)))
+    for i in range(rotary_dim // 2):
+        angle = positions * base ** (-2.0 * i / rotary_dim)
+        u, v = x[..., 2 * i], x[..., 2 * i + 1]
+        out[..., 2 * i] = u * torch.cos(angle) - v * torch.sin(angle)
+        out[..., 2 * i + 1] = v * torch.cos(angle) + u * torch.sin(angle)
     return out
 
 
 def windowed_softmax_attention(q, k, v, scale, window):
     """One head: `q`, `k` [tokens, dim], `v` [tokens, vdim]; token i sees j with 0 <= i - j < window."""
     tokens = q.shape[0]
-    out = torch.zeros((tokens, v.shape[1]), dtype=F)
-    for i in range(tokens):
-        first = max(0, i - window + 1)
-        scores = (k[first : i + 1] @ q[i]) * scale
-        out[i] = torch.softmax(scores, 0) @ v[first : i + 1]
-    return out
+    distance = torch.arange(tokens).view(-1, 1) - torch.arange(tokens).view(1, -1)          # i - j
+    scores = (q @ k.T) * scale
+    scores = scores.masked_fill((distance < 0) | (distance >= window), float("-inf"))
+    return torch.softmax(scores, dim=-1) @ v
 
 
 def differential_attention(h, weights, prefix, mixer, eps):
@@ -94,15 +91,14 @@ def dense_feed_forward(h, weights, prefix):
 def routed_feed_forward(h, weights, prefix, mlp):
     experts, top = mlp["router"]["experts"], mlp["router"]["top"]
     logits = h @ weights[f"{prefix}.router"].T + weights[f"{prefix}.router.b"]
+    chosen = torch.topk(logits, top, dim=-1).indices                  # the largest logits
+    share = torch.zeros_like(logits).scatter(1, chosen, torch.softmax(torch.gather(logits, 1, chosen), dim=-1))
     out = torch.zeros_like(h)
-    for t in range(h.shape[0]):
-        chosen = sorted(range(experts), key=lambda e: (-float(logits[t, e]), e))[:top]
-        share = torch.softmax(logits[t, chosen], 0)
-        for place, expert in enumerate(chosen):
-            name = f"{prefix}.e{expert}"
-            gate = h[t] @ weights[f"{name}.gate"].T
-            inner = gate * torch.sigmoid(gate) * (h[t] @ weights[f"{name}.up"].T)
-            out[t] += share[place] * (inner @ weights[f"{name}.down"].T)
+    for expert in range(experts):                                      # every expert on every token, weighted by zero where not chosen
+        name = f"{prefix}.e{expert}"
+        gate = h @ weights[f"{name}.gate"].T
+        inner = gate * torch.sigmoid(gate) * (h @ weights[f"{name}.up"].T)
+        out += share[:, expert : expert + 1] * (inner @ weights[f"{name}.down"].T)
     return out
 
 
