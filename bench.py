@@ -291,9 +291,31 @@ def fasesun_sizes():
     }
 
 
+def bisudra_sizes():
+    """Layer sizes that resemble a real model of Bisudra's kind (differential attention with 64-element maps over 128-element values and a
+    window of 1,024 positions; dense feed-forwards four times the width alternating with 32 experts of which 4 are chosen), and for each a
+    dense Qwen3 of the same width, depth, vocabulary, query width and key/value bytes per position whose feed-forward holds as many
+    weights as the ones one token passes."""
+    def bisudra(width, heads, expert_ff):
+        mixer = {"heads": heads, "kv_heads": 8, "dim": 64, "vdim": 128, "diff": 0.5, "scale": 0.125, "mask": {"size": 1024}, "rot": {"base": 10000.0, "dims": 64}}
+        dense = {"type": "attention", "mixer": mixer, "mlp": {"kind": "dense", "ff": 4 * width}}
+        routed = {"type": "attention", "mixer": mixer, "mlp": {"kind": "moe", "router": {"experts": 32, "top": 4}, "expert": {"ff": expert_ff}}}
+        return {"architecture": "Bisudra", "canon": {"taps": 4}, "layers": [dense, routed, dense, routed], "norm": {"eps": 1e-5}, "token_side": {"dim": 64},
+                "vocab": 32768, "width": width}
+
+    def dense(width, heads, intermediate):
+        return dict(qwen3(4, width, heads, 8, intermediate, True), vocab_size=32768)
+
+    return {
+        "1024": (bisudra(1024, 8, 704), dense(1024, 8, 2752)),
+        "2048": (bisudra(2048, 16, 1344), dense(2048, 16, 5440)),
+        "4096": (bisudra(4096, 32, 2752), dense(4096, 32, 10944)),
+    }
+
+
 def design_comparison(args) -> int:
-    """`--design fasesun`: prefill and decode throughput of Fasesun layers at three real sizes beside a dense Qwen3 of equal width,
-    depth and active feed-forward width, with the device time of each kernel class in one prompt step and one decode step."""
+    """`--design fasesun|bisudra`: prefill and decode throughput of the design's layers at three real sizes beside a dense Qwen3 of equal
+    width, depth and active feed-forward width, with the device time of each kernel class in one prompt step and one decode step."""
     import numpy as np
     import torch
 
@@ -308,9 +330,10 @@ def design_comparison(args) -> int:
     records = []
     clocks = ClockSampler()
     clocks.start()
-    for size, (design_config, dense_config) in fasesun_sizes().items():
+    sizes = bisudra_sizes() if args.design == "bisudra" else fasesun_sizes()
+    for size, (design_config, dense_config) in sizes.items():
         record = {"size": size, "batch": batch, "context": context}
-        for label, config in (("fasesun", design_config), ("qwen3", dense_config)):
+        for label, config in ((args.design, design_config), ("qwen3", dense_config)):
             model = tau_rs_b200.random_model(config, seed=0, dtype="bfloat16", device="cuda:0")
             vocab = model.spec.vocab_size
             engine = Engine(model, max_tokens=batch * (context + 256), max_sequence_tokens=context + 256)
@@ -357,12 +380,12 @@ def design_comparison(args) -> int:
             decode_once()
             decode_classes = kernels.take_timing(stop=True)
             read = engine.bytes_read_by_a_decode_step()
-            if label == "fasesun":
+            if label != "qwen3":
                 # `bytes_read_by_a_decode_step` counts the experts that one token chooses; a batch whose tokens choose independently
                 # reads E (1 - (1 - top / E)^batch) of a layer's E experts on average.
                 for layer in config["layers"]:
                     mlp = layer.get("mlp")
-                    if mlp:
+                    if mlp and "router" in mlp:
                         experts, top = mlp["router"]["experts"], mlp["router"]["top"]
                         distinct = experts * (1.0 - (1.0 - top / experts) ** batch)
                         read += int((distinct - top) * 3 * mlp["expert"]["ff"] * config["width"] * 2)
@@ -377,7 +400,7 @@ def design_comparison(args) -> int:
             del engine, model
             torch.cuda.empty_cache()
         records.append(record)
-    print(json.dumps({"design": "fasesun", "beside": "qwen3 of equal width, depth and active feed-forward width", "dtype": "bf16", "data": "synthetic",
+    print(json.dumps({"design": args.design, "beside": "qwen3 of equal width, depth and active feed-forward width", "dtype": "bf16", "data": "synthetic",
                       "peaks": peaks, "sizes": records, "clocks": clocks.stop()}))
     return 0
 
@@ -397,7 +420,7 @@ def main() -> int:
     parser.add_argument("--sections", default="prefill,decode,points,e2e",
                         help="which measurements to run: prefill, decode, points, e2e, kernels (the counterparts of the reference arm's kernels), "
                              "classes (time per kernel class of a decode step, outside a graph)")
-    parser.add_argument("--design", default="", choices=["", "fasesun"],
+    parser.add_argument("--design", default="", choices=["", "fasesun", "bisudra"],
                         help="instead of the default workload: layers of this design at real sizes beside a dense Qwen3 of equal size")
     args = parser.parse_args()
 

@@ -116,7 +116,10 @@ class SequenceCache:
         kv_needs = [need for need, _ in groups.values() if need.kind in ("kv", "rows")]
         bounded = all(need.window for need in kv_needs)
         self.widest_window = max((need.window for need in kv_needs), default=0) if bounded else None
-        self.pages_per_sequence = pages_for(max_sequence_tokens) if bounded else min(self.n_pages, pages_for(max_sequence_tokens))
+        # ... but its page table is addressed by position, so a sequence is given at most 64 times the pages of the whole cache
+        # (1,024 at least), not the 2^31 positions that a design without a position limit would allow.
+        self.pages_per_sequence = (min(pages_for(max_sequence_tokens), max(64 * self.n_pages, 1024)) if bounded
+                                   else min(self.n_pages, pages_for(max_sequence_tokens)))
         self.max_sequence_tokens = min(max_sequence_tokens, self.pages_per_sequence * PAGE_TOKENS)
         self.n_slots = min(self.n_pages, max_slots) if max_slots else self.n_pages
         self.slots = FreeList(self.n_slots, "sequence slot")

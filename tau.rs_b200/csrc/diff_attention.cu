@@ -155,7 +155,144 @@ diff_attention_kernel(const T* __restrict__ queries, const T* __restrict__ rows,
     }
 }
 
+// The same preparation for the cache of ordinary heads: every map is a head of its own, `wide` = max(dim, vdim) elements,
+// zeros behind what it holds.  Query (head, map) goes to slot (group * 2 + map) * (heads / kv_heads) + head % (heads / kv_heads)
+// of queries [tokens, 2 * heads, wide], so that the slots of one key/value head (group, map) lie together; key pages
+// [pages, 2 * kv_heads, page_tokens, wide] hold map `map` of group `group` under head group * 2 + map, value pages hold the
+// group's values under both.
+template <typename T>
+__global__ void __launch_bounds__(kWarps * 32)
+diff_prepare_wide_kernel(const T* __restrict__ projected, long long projected_stride, const float* __restrict__ q_weight, const float* __restrict__ k_weight,
+                         float eps, const float* __restrict__ inv_freq, int rotary, T* __restrict__ queries, T* __restrict__ key_pages,
+                         T* __restrict__ value_pages, const int* __restrict__ positions, const int* __restrict__ token_seq,
+                         const int* __restrict__ page_rows, int page_stride, int page_tokens, int heads, int kv_heads, int dim, int vdim, int wide,
+                         int write_cache) {
+    grid_dependents_launch();
+    grid_dependency_wait();
+    const int token = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int position = positions[token];
+    const T* source_row = projected + static_cast<size_t>(token) * projected_stride;
+    size_t page_base = 0;
+    if (write_cache) {
+        const int page = page_rows[static_cast<size_t>(token_seq[token]) * page_stride + position / page_tokens];
+        page_base = static_cast<size_t>(page) * 2 * kv_heads * page_tokens * wide + static_cast<size_t>(position % page_tokens) * wide;
+    }
+    const size_t head_pitch = static_cast<size_t>(page_tokens) * wide;
+    const int q_maps = heads * 2, maps = q_maps + (write_cache ? kv_heads * 2 : 0), per_group = heads / kv_heads;
+    for (int map = warp; map < maps; map += kWarps) {
+        const bool is_query = map < q_maps;
+        const T* source = source_row + static_cast<size_t>(map) * dim;
+        T* target;
+        if (is_query) {
+            const int head = map >> 1, which = map & 1;
+            const int slot = ((head / per_group) * 2 + which) * per_group + head % per_group;
+            target = queries + (static_cast<size_t>(token) * q_maps + slot) * wide;
+        } else {
+            target = key_pages + page_base + static_cast<size_t>(map - q_maps) * head_pitch;
+        }
+        const float* weight = is_query ? q_weight : k_weight;
+        float squares = 0.0f;
+        for (int column = lane; column < dim; column += 32) {
+            const float value = to_float(source[column]);
+            squares += value * value;
+        }
+        const float inverse = 1.0f / sqrtf(warp_sum(squares) / static_cast<float>(dim) + eps);
+        for (int pair = lane; 2 * pair < wide; pair += 32) {
+            const int first = 2 * pair;
+            float u = first < dim ? to_float(source[first]) * inverse * weight[first] : 0.0f;
+            float w = first + 1 < dim ? to_float(source[first + 1]) * inverse * weight[first + 1] : 0.0f;
+            if (first + 1 < rotary) {
+                float sine, cosine;
+                sincosf(static_cast<float>(position) * inv_freq[pair], &sine, &cosine);
+                const float a = u * cosine - w * sine, b = w * cosine + u * sine;
+                u = a; w = b;
+            }
+            target[first] = from_float<T>(u);
+            if (first + 1 < wide) target[first + 1] = from_float<T>(w);
+        }
+    }
+    if (write_cache) {
+        const T* values = source_row + static_cast<size_t>(q_maps + kv_heads * 2) * dim;
+        for (int item = threadIdx.x; item < kv_heads * 2 * wide; item += blockDim.x) {
+            const int head = item / wide, column = item % wide;
+            value_pages[page_base + static_cast<size_t>(head) * head_pitch + column] = column < vdim ? values[(head >> 1) * vdim + column] : from_float<T>(0.0f);
+        }
+    }
+}
+
+// grid: tokens; a warp per head.  attended [tokens, 2 * heads, wide] in the slots of the kernel above.
+template <typename T>
+__global__ void __launch_bounds__(kWarps * 32)
+diff_combine_kernel(const T* __restrict__ attended, const T* __restrict__ gate, long long gate_stride, T* __restrict__ out, int heads, int kv_heads,
+                    int vdim, int wide, float lambda, float eps, float post_scale) {
+    grid_dependents_launch();
+    grid_dependency_wait();
+    const int token = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, per_group = heads / kv_heads;
+    for (int head = warp; head < heads; head += kWarps) {
+        const int slot = (head / per_group) * 2 * per_group + head % per_group;
+        const T* first = attended + (static_cast<size_t>(token) * 2 * heads + slot) * wide;
+        const T* second = first + static_cast<size_t>(per_group) * wide;
+        float held[kMaxOwned];
+        float squares = 0.0f;
+#pragma unroll
+        for (int i = 0; i < kMaxOwned; ++i) {
+            const int column = lane + 32 * i;
+            held[i] = column < vdim ? to_float(first[column]) - lambda * to_float(second[column]) : 0.0f;
+            squares += held[i] * held[i];
+        }
+        const float inverse = post_scale / sqrtf(warp_sum(squares) / static_cast<float>(vdim) + eps);
+#pragma unroll
+        for (int i = 0; i < kMaxOwned; ++i) {
+            const int column = lane + 32 * i;
+            if (column < vdim) {
+                float value = held[i] * inverse;
+                if (gate) value *= sigmoid(to_float(gate[static_cast<size_t>(token) * gate_stride + head * vdim + column]));
+                out[(static_cast<size_t>(token) * heads + head) * vdim + column] = from_float<T>(value);
+            }
+        }
+    }
+}
+
 }  // namespace
+
+TAU_EXPORT int tau_diff_prepare_wide(int dtype, const void* projected, long long projected_stride, const float* q_weight, const float* k_weight, float eps,
+                                     const float* inv_freq, int rotary, void* queries, void* key_pages, void* value_pages, const int* positions,
+                                     const int* token_seq, const int* page_rows, int page_stride, int page_tokens, int tokens, int heads, int kv_heads,
+                                     int dim, int vdim, int wide, int write_cache, void* stream) {
+    if (tokens <= 0) return 0;
+    if (!projected || !q_weight || !k_weight || !queries || !positions || heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0 || dim <= 0 || vdim <= 0
+        || wide < dim || wide < vdim || (wide & 1) || rotary < 0 || rotary > dim || (rotary & 1) || (rotary > 0 && !inv_freq)
+        || (write_cache && (!key_pages || !value_pages || !token_seq || !page_rows)))
+        return cudaErrorInvalidValue;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (dtype == TAU_F32)
+        tau_launch(diff_prepare_wide_kernel<float>, dim3(tokens), dim3(kWarps * 32), 0, s, static_cast<const float*>(projected), projected_stride, q_weight,
+                   k_weight, eps, inv_freq, rotary, static_cast<float*>(queries), static_cast<float*>(key_pages), static_cast<float*>(value_pages), positions,
+                   token_seq, page_rows, page_stride, page_tokens, heads, kv_heads, dim, vdim, wide, write_cache);
+    else if (dtype == TAU_BF16)
+        tau_launch(diff_prepare_wide_kernel<bf16>, dim3(tokens), dim3(kWarps * 32), 0, s, static_cast<const bf16*>(projected), projected_stride, q_weight,
+                   k_weight, eps, inv_freq, rotary, static_cast<bf16*>(queries), static_cast<bf16*>(key_pages), static_cast<bf16*>(value_pages), positions,
+                   token_seq, page_rows, page_stride, page_tokens, heads, kv_heads, dim, vdim, wide, write_cache);
+    else
+        return cudaErrorInvalidValue;
+    return tau_launch_status();
+}
+
+TAU_EXPORT int tau_diff_combine(int dtype, const void* attended, const void* gate, long long gate_stride, void* out, int tokens, int heads, int kv_heads,
+                                int vdim, int wide, float lambda, float eps, float post_scale, void* stream) {
+    if (tokens <= 0) return 0;
+    if (!attended || !out || heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0 || vdim <= 0 || vdim > 32 * kMaxOwned || wide < vdim) return cudaErrorInvalidValue;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (dtype == TAU_F32)
+        tau_launch(diff_combine_kernel<float>, dim3(tokens), dim3(kWarps * 32), 0, s, static_cast<const float*>(attended), static_cast<const float*>(gate),
+                   gate_stride, static_cast<float*>(out), heads, kv_heads, vdim, wide, lambda, eps, post_scale);
+    else if (dtype == TAU_BF16)
+        tau_launch(diff_combine_kernel<bf16>, dim3(tokens), dim3(kWarps * 32), 0, s, static_cast<const bf16*>(attended), static_cast<const bf16*>(gate),
+                   gate_stride, static_cast<bf16*>(out), heads, kv_heads, vdim, wide, lambda, eps, post_scale);
+    else
+        return cudaErrorInvalidValue;
+    return tau_launch_status();
+}
 
 TAU_EXPORT int tau_diff_prepare(int dtype, const void* projected, long long projected_stride, const float* q_weight, const float* k_weight, float eps,
                                 const float* inv_freq, int rotary, void* queries, void* rows, const int* positions, const int* token_seq,

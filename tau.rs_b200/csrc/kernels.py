@@ -84,7 +84,7 @@ _CLASS_OF = {
     "sample_gumbel": "selection", "store_words_host": "selection", "random_normal": "other",
     "stream_add_norm": "norm", "gated_group_norm": "norm", "gemm_simt_batched": "product", "linear_recurrence": "recurrence",
     "latent_prepare": "attention", "latent_attention": "attention", "latent_expand": "attention", "moe_route": "routing", "moe_gate_up": "experts", "moe_down": "experts", "gemm_tc_groups": "experts", "moe_sort": "routing", "moe_gather": "routing",
-    "moe_combine": "routing", "diff_prepare": "attention", "diff_attention": "attention", "causal_taps": "norm", "gated_add_norm": "norm",
+    "moe_combine": "routing", "diff_prepare": "attention", "diff_attention": "attention", "diff_combine": "attention", "causal_taps": "norm", "gated_add_norm": "norm",
     "side_gate": "activation", "unit_add_mix": "norm", "norm_rows": "norm", "relu_squared": "activation",
 }
 _timing = None     # while timing: [last event, [(class, event after the launch), ...]]
@@ -898,12 +898,62 @@ def diff_attention(queries, rows, gate, out, step, page_rows, n_kv_heads: int, v
         ctypes.c_int(window), ctypes.c_float(lam), ctypes.c_float(eps), ctypes.c_float(post_scale), _stream()), "diff_attention")
 
 
+def diff_prepare_wide(projected, q_weight, k_weight, eps: float, inv_freq, rotary_dim: int, queries, key_pages, value_pages, positions, token_seq,
+                      page_rows, n_heads: int, n_kv_heads: int, dim: int, vdim: int, write_cache: bool = True) -> None:
+    """As `diff_prepare`, for the cache of ordinary heads: every map becomes a head of `wide` = `queries.shape[2]` >= max(dim, vdim)
+    elements, zeros behind what it holds.  `queries` [tokens, 2 * n_heads, wide] holds query (head, map) in slot
+    `(group * 2 + map) * (n_heads / n_kv_heads) + head % (n_heads / n_kv_heads)`; `key_pages` and `value_pages`
+    [pages, 2 * n_kv_heads, 64, wide] hold key (group, map) under head `group * 2 + map` and the group's values under both, so
+    that grouped-query attention over 2 * n_heads heads and 2 * n_kv_heads key/value heads computes both maps of every head."""
+    _on_device(projected, q_weight, k_weight, inv_freq, queries, key_pages, value_pages, positions, token_seq, page_rows)
+    tokens, wide = projected.shape[0], queries.shape[2]
+    _require(projected.shape[1] >= n_heads * 2 * dim + n_kv_heads * (2 * dim + vdim) and projected.stride(1) == 1, "the projection is too narrow")
+    _require(queries.shape == (tokens, 2 * n_heads, wide) and queries.is_contiguous() and queries.dtype == projected.dtype and wide >= max(dim, vdim)
+             and wide % 2 == 0, "queries must be [tokens, 2 * n_heads, wide]")
+    _f32_vector(q_weight, dim, "the query norm weight")
+    _f32_vector(k_weight, dim, "the key norm weight")
+    _require(rotary_dim % 2 == 0 and 0 <= rotary_dim <= dim, "rotary_dim must be even and at most dim")
+    if rotary_dim:
+        _f32_vector(inv_freq, rotary_dim // 2, "the rotation's frequencies")
+    _int_vector(positions, "positions")
+    if write_cache:
+        _int_vector(token_seq, "token_seq")
+        for pages in (key_pages, value_pages):
+            _require(pages.shape[1:] == (2 * n_kv_heads, PAGE_TOKENS, wide) and pages.is_contiguous() and pages.dtype == projected.dtype,
+                     "cache pages must be [pages, 2 * n_kv_heads, 64, wide]")
+        _require(page_rows.dtype == torch.int32 and page_rows.dim() == 2 and page_rows.is_contiguous(), "page rows must be int32 [sequences, stride]")
+    library = build.load_library("diff_attention.cu")
+    _check(library.tau_diff_prepare_wide(
+        _code(projected), _pointer(projected), ctypes.c_longlong(projected.stride(0)), _pointer(q_weight), _pointer(k_weight), ctypes.c_float(eps),
+        _pointer(inv_freq), ctypes.c_int(rotary_dim), _pointer(queries), _pointer(key_pages if write_cache else None),
+        _pointer(value_pages if write_cache else None), _pointer(positions), _pointer(token_seq), _pointer(page_rows),
+        ctypes.c_int(page_rows.shape[1] if write_cache else 0), ctypes.c_int(PAGE_TOKENS), ctypes.c_int(tokens), ctypes.c_int(n_heads), ctypes.c_int(n_kv_heads),
+        ctypes.c_int(dim), ctypes.c_int(vdim), ctypes.c_int(wide), ctypes.c_int(1 if write_cache else 0), _stream()), "diff_prepare")
+
+
+def diff_combine(attended, gate, out, n_heads: int, n_kv_heads: int, vdim: int, lam: float, eps: float, post_scale: float) -> None:
+    """`attended` [tokens, 2 * n_heads, wide] in the slots of `diff_prepare_wide`: per head `o = map 1 - lam * map 2` over the first
+    `vdim` elements, divided by its root mean square (eps inside the root), times `post_scale`, times `sigmoid(gate)` (or no gate);
+    `out` [tokens, n_heads * vdim].  32-bit throughout, one rounding."""
+    _on_device(attended, gate, out)
+    tokens, _, wide = attended.shape
+    _require(attended.shape[1] == 2 * n_heads and attended.is_contiguous() and out.shape == (tokens, n_heads * vdim) and out.is_contiguous()
+             and out.dtype == attended.dtype, "attended must be [tokens, 2 * n_heads, wide] and the output [tokens, n_heads * vdim]")
+    _require(vdim <= DIFF_MAX_VALUE_DIM and vdim <= wide, f"values may have at most {DIFF_MAX_VALUE_DIM} elements per head")
+    if gate is not None:
+        _require(gate.shape == out.shape and gate.dtype == out.dtype and gate.stride(1) == 1, "the gate must have the output's shape and dtype")
+    library = build.load_library("diff_attention.cu")
+    _check(library.tau_diff_combine(_code(out), _pointer(attended), _pointer(gate), ctypes.c_longlong(0 if gate is None else gate.stride(0)), _pointer(out),
+                                    ctypes.c_int(tokens), ctypes.c_int(n_heads), ctypes.c_int(n_kv_heads), ctypes.c_int(vdim), ctypes.c_int(wide),
+                                    ctypes.c_float(lam), ctypes.c_float(eps), ctypes.c_float(post_scale), _stream()), "diff_combine")
+
+
 # ---------------------------------------------------------------------------- sublayer arrangement on a 32-bit stream
 def causal_taps(stream, weight, state, step, read_out, plain_out=None, update: bool = True) -> None:
     """`read_out[t] = stream[t] + sum_j weight[:, j] * stream[t - taps + 1 + j]` over each sequence's run of the step, the rows before
     the run's first token taken from `state[slot]` ([slots, taps - 1, width] float32: the sequence's last inputs, zeros at its start);
     `plain_out` (optional) receives `stream` itself in the output's dtype.  With `update` the state then becomes the last `taps - 1`
-    inputs of each sequence (a second launch)."""
+    inputs of each sequence (a second launch, or the same one where every sequence brings one token)."""
     _on_device(stream, weight, state, read_out, plain_out)
     tokens, width = stream.shape
     taps = 0 if weight is None else weight.shape[1]      # without a weight the outputs are the stream itself, rounded
@@ -917,10 +967,12 @@ def causal_taps(stream, weight, state, step, read_out, plain_out=None, update: b
     _require(read_out.shape == stream.shape and read_out.is_contiguous(), "the output must match the stream")
     if plain_out is not None:
         _require(plain_out.shape == stream.shape and plain_out.is_contiguous() and plain_out.dtype == read_out.dtype, "the plain output must match the other")
+    single = bool(getattr(step, "all_single", False)) and tokens == step.n_seqs
     library = build.load_library("sublayer.cu")
     _check(library.tau_causal_taps(_code(read_out), _pointer(stream), _pointer(weight), _pointer(state), _pointer(step.token_seq), _pointer(step.cu_seqlens),
                                    _pointer(step.seq_slot), _pointer(read_out), _pointer(plain_out), ctypes.c_int(tokens), ctypes.c_int(step.n_seqs),
-                                   ctypes.c_int(width), ctypes.c_int(taps), ctypes.c_int(1 if update else 0), _stream()), "causal_taps", 2 if update else 1)
+                                   ctypes.c_int(width), ctypes.c_int(taps), ctypes.c_int(1 if update else 0), ctypes.c_int(1 if single else 0), _stream()),
+           "causal_taps", 2 if update and not single else 1)
 
 
 def gated_add_norm(source, target, branch, gate, weight, bias, eps: float, centred: bool, copy_out=None) -> None:

@@ -24,15 +24,17 @@ __device__ __forceinline__ float load_as_float(const void* base, int code, size_
 __device__ __forceinline__ float sigmoid(float z) { return 1.0f / (1.0f + expf(-z)); }
 
 // grid: tokens.  state [slots, taps - 1, width]; row `taps - 1 + s` of it stands for the sequence's input at run-local index s < 0.
+// `shift_state`: every sequence brings one token, so the block of a token is the only reader of its sequence's state and moves it
+// on itself (each thread the channels it has just read): rows go down by one and the token becomes the last.
 template <typename T>
 __global__ void __launch_bounds__(kThreads)
-causal_taps_kernel(const float* __restrict__ x, const float* __restrict__ weight, const float* __restrict__ state, const int* __restrict__ token_seq,
+causal_taps_kernel(const float* __restrict__ x, const float* __restrict__ weight, float* state, const int* __restrict__ token_seq,
                    const int* __restrict__ cu_seqlens, const int* __restrict__ seq_slot, T* __restrict__ read_out, T* __restrict__ plain_out,
-                   int width, int taps) {
+                   int width, int taps, int shift_state) {
     grid_dependents_launch();
     grid_dependency_wait();
     const int token = blockIdx.x, seq = token_seq[token], first = cu_seqlens[seq], local = token - first;
-    const float* kept = state + static_cast<size_t>(seq_slot[seq]) * (taps - 1) * width;
+    float* kept = state + static_cast<size_t>(seq_slot[seq]) * (taps - 1) * width;
     for (int column = threadIdx.x; column < width; column += blockDim.x) {
         const float own = x[static_cast<size_t>(token) * width + column];
         float sum = 0.0f;
@@ -44,6 +46,10 @@ causal_taps_kernel(const float* __restrict__ x, const float* __restrict__ weight
         }
         read_out[static_cast<size_t>(token) * width + column] = from_float<T>(own + sum);
         if (plain_out) plain_out[static_cast<size_t>(token) * width + column] = from_float<T>(own);
+        if (shift_state) {
+            for (int i = 0; i + 2 < taps; ++i) kept[static_cast<size_t>(i) * width + column] = kept[static_cast<size_t>(i + 1) * width + column];
+            kept[static_cast<size_t>(taps - 2) * width + column] = own;
+        }
     }
 }
 
@@ -202,20 +208,21 @@ int allow_shared(Kernel kernel, size_t bytes) {
 
 TAU_EXPORT int tau_causal_taps(int dtype, const float* x, const float* weight, float* state, const int* token_seq, const int* cu_seqlens,
                                const int* seq_slot, void* read_out, void* plain_out, int tokens, int sequences, int width, int taps, int update,
-                               void* stream) {
+                               int all_single, void* stream) {
     if (tokens <= 0) return 0;
     if (!x || (!weight && taps > 0) || (!state && taps > 1) || !token_seq || !cu_seqlens || !seq_slot || !read_out || sequences <= 0 || width <= 0 || taps < 0) return cudaErrorInvalidValue;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int shift = (update && taps > 1 && all_single && tokens == sequences) ? 1 : 0;
     if (dtype == TAU_F32)
-        tau_launch(causal_taps_kernel<float>, dim3(tokens), dim3(kThreads), 0, s, x, weight, static_cast<const float*>(state), token_seq, cu_seqlens, seq_slot,
-                   static_cast<float*>(read_out), static_cast<float*>(plain_out), width, taps);
+        tau_launch(causal_taps_kernel<float>, dim3(tokens), dim3(kThreads), 0, s, x, weight, state, token_seq, cu_seqlens, seq_slot,
+                   static_cast<float*>(read_out), static_cast<float*>(plain_out), width, taps, shift);
     else if (dtype == TAU_BF16)
-        tau_launch(causal_taps_kernel<bf16>, dim3(tokens), dim3(kThreads), 0, s, x, weight, static_cast<const float*>(state), token_seq, cu_seqlens, seq_slot,
-                   static_cast<bf16*>(read_out), static_cast<bf16*>(plain_out), width, taps);
+        tau_launch(causal_taps_kernel<bf16>, dim3(tokens), dim3(kThreads), 0, s, x, weight, state, token_seq, cu_seqlens, seq_slot,
+                   static_cast<bf16*>(read_out), static_cast<bf16*>(plain_out), width, taps, shift);
     else
         return cudaErrorInvalidValue;
     int status = tau_launch_status();
-    if (status != 0 || !update || taps < 2) return status;
+    if (status != 0 || !update || taps < 2 || shift) return status;
     tau_launch(taps_state_kernel, dim3(sequences), dim3(kThreads), 0, s, x, state, cu_seqlens, seq_slot, width, taps);
     return tau_launch_status();
 }

@@ -22,6 +22,7 @@ from typing import Sequence
 import numpy as np
 import torch
 
+from ..cache.sequence_cache import pages_for
 from ..csrc import kernels
 from .batch import StepEntry, StepLayout, step_views
 
@@ -35,8 +36,8 @@ class _DecodeGraph:
     token-to-sequence map, run bounds) are made once; a step fills in tokens, positions, slots, lengths and page rows.
     """
 
-    def __init__(self, engine, n_seqs: int, splits: int):
-        self.stride = engine.cache.pages_per_sequence
+    def __init__(self, engine, n_seqs: int, splits: int, stride: int):
+        self.stride = stride
         self.layout = StepLayout(n_seqs, n_seqs, n_seqs, {group: self.stride for group in engine.cache.kv})
         self.buffer = torch.zeros(self.layout.total, dtype=torch.int32, device=engine.device)
         self.context = step_views(self.layout, self.buffer, 1, 1, True)
@@ -72,10 +73,15 @@ def run_decode_graph(engine, entries: Sequence[StepEntry], starts: Sequence[int]
     splits = engine._split_choice.get(bucket)
     if splits is None:
         splits = engine._split_choice[bucket] = engine.decode_splits(len(entries), max_len)
-    key = (len(entries), splits)
+    # Table rows of a sequence's pages: all that a sequence may ever hold, unless sequences may outgrow the cache (every group has
+    # a window); then as many as the longest sequence of the step needs, by powers of two, and the number is part of the key.
+    stride = engine.cache.pages_per_sequence
+    if engine.cache.widest_window is not None:
+        stride = min(stride, pages_for(1 << bucket[1]))
+    key = (len(entries), splits, stride)
     state = engine._graphs.pop(key, None)
     if state is None:
-        state = _DecodeGraph(engine, len(entries), splits)
+        state = _DecodeGraph(engine, len(entries), splits, stride)
         while len(engine._graphs) >= MAX_GRAPHS:
             engine._graphs.pop(next(iter(engine._graphs)))     # the least recently used: a dict keeps its order
     engine._graphs[key] = state                                 # (re-)inserted as the most recent

@@ -44,13 +44,15 @@ def test_blocks_schedule_and_cache_groups():
     groups = DecoderModel(spec, torch.float32, "cpu").cache_groups()
     assert groups["taps"][0].kind == "state" and groups["taps"][0].state_shape == (2, 96) and groups["taps"][1] == 4
     rows = sorted((need.row_width, need.window, layers) for name, (need, layers) in groups.items() if need.kind == "rows")
-    assert rows == sorted([(2 * (2 * 16 + 24), 37, 1), (2 * (2 * 24 + 16), 130, 1), (3 * (2 * 8 + 40), 70, 1), (2 * 32 + 32, 64, 1)])
+    assert rows == sorted([(2 * (2 * 16 + 24), 37, 1), (2 * (2 * 24 + 16), 130, 1), (3 * (2 * 8 + 40), 70, 1)])
+    # Where the wider of a key and a value is a multiple of 16, every map is an ordinary head of that width: 2 key/value heads per group.
+    assert [(need.n_kv_heads, need.head_dim, need.window, layers) for need, layers in groups.values() if need.kind == "kv"] == [(2, 32, 64, 1)]
 
 
 def test_one_tap_keeps_no_state():
     spec = spec_from_config_json(bm.ONE_TAP)
     assert all(entry.extra_cache == () for entry in spec.schedule)
-    assert all(need.kind == "rows" for need, _ in DecoderModel(spec, torch.float32, "cpu").cache_groups().values())
+    assert all(need.kind in ("rows", "kv") for need, _ in DecoderModel(spec, torch.float32, "cpu").cache_groups().values())
 
 
 def test_the_model_asks_for_exactly_the_tensors_of_the_design():

@@ -71,7 +71,8 @@ def packed_step(runs, slots):
     bounds = np.concatenate([[0], np.cumsum(runs)]).astype(np.int32)
     token_seq = np.concatenate([np.full(count, index, dtype=np.int32) for index, count in enumerate(runs)])
     as_device = lambda values: torch.tensor(np.asarray(values, dtype=np.int32), device=DEVICE)
-    return SimpleNamespace(n_seqs=len(runs), token_seq=as_device(token_seq), cu_seqlens=as_device(bounds), seq_slot=as_device(slots))
+    return SimpleNamespace(n_seqs=len(runs), token_seq=as_device(token_seq), cu_seqlens=as_device(bounds), seq_slot=as_device(slots),
+                           all_single=all(count == 1 for count in runs))
 
 
 # ---- each mechanism's kernels alone -----------------------------------------------------------------------------------
@@ -89,7 +90,7 @@ def test_causal_taps_carry_their_tail_from_step_to_step(dtype, taps):
     if state is not None:
         state[slots] = 0.0          # a sequence starts from zeros, as the cache leaves a slot
     history = [torch.zeros(0, width, dtype=torch.float64) for _ in slots]
-    for runs in ([1, 9, 2], [1, 1, 1], [2, 1, 6], [5, 2, 1]):
+    for runs in ([1, 9, 2], [1, 1, 1], [1, 1, 1], [2, 1, 6], [1, 1, 1], [5, 2, 1]):      # steps of single tokens move the state in the same launch
         new = [torch.randn(count, width, dtype=torch.float64).float().double() for count in runs]
         x = on_device(torch.cat(new))
         read = torch.empty(x.shape, dtype=TORCH[dtype], device=DEVICE)
@@ -194,31 +195,53 @@ def test_a_router_with_a_bias_weighs_by_the_softmax_of_the_chosen_logits(experts
     assert experts == top or not torch.equal(without, chosen)                # the bias moves the choice
 
 
-def run_attention_kernels(h, W, mixer, eps, dtype, positions, page_of, cache_rows):
-    """`h` [tokens, width] through the library's projection-free path: the stacked projection in 64-bit, then the prepare and
-    attention kernels over a paged cache whose pages are `page_of[position // 64]`."""
+def attention_cache(mixer, pages, dtype, fill):
+    """Pages for one layer in the layout that the sizes choose: keys and values of ordinary heads where max(dim, vdim) is a multiple
+    of 16, else one row per position."""
+    kv_heads, dim, vdim = mixer["kv_heads"], mixer["dim"], mixer["vdim"]
+    wide = max(dim, vdim)
+    if wide % 16 == 0:
+        return tuple(torch.full((pages, 2 * kv_heads, 64, wide), fill, dtype=TORCH[dtype], device=DEVICE) for _ in range(2))
+    return torch.full((pages, 64, kv_heads * (2 * dim + vdim)), fill, dtype=TORCH[dtype], device=DEVICE)
+
+
+def run_attention_kernels(h, W, mixer, eps, dtype, positions, page_of, cache):
+    """`h` [tokens, width] of one sequence through the stacked projection in 64-bit, then the library's kernels over a paged cache
+    whose pages are `page_of[position // 64]`, in the layout of `cache` (see `attention_cache`)."""
     from tau_rs_b200.csrc import kernels
 
     heads, kv_heads, dim, vdim = mixer["heads"], mixer["kv_heads"], mixer["dim"], mixer["vdim"]
     stacked = torch.cat([W["m.q"], W["m.k"], W["m.v"], W["m.g"]]).double()
     projected = on_device(h.double() @ stacked.T, TORCH[dtype])
     tokens = h.shape[0]
-    queries = torch.empty((tokens, heads, 2, dim), dtype=TORCH[dtype], device=DEVICE)
     rotary = mixer["rot"]["dims"]
     inv_freq = torch.tensor([mixer["rot"]["base"] ** (-2.0 * i / rotary) for i in range(rotary // 2)], dtype=torch.float64).float().to(DEVICE) if rotary else None
-    step = SimpleNamespace(positions=torch.tensor(positions, dtype=torch.int32, device=DEVICE), token_seq=torch.zeros(tokens, dtype=torch.int32, device=DEVICE))
-    pages = torch.tensor([page_of], dtype=torch.int32, device=DEVICE)
-    kernels.diff_prepare(projected, on_device(W["m.q.norm"]), on_device(W["m.k.norm"]), eps, inv_freq, rotary, queries, cache_rows, step.positions, step.token_seq,
-                         pages, heads, kv_heads, dim, vdim)
+    as_device = lambda values: torch.tensor(values, dtype=torch.int32, device=DEVICE)
+    step = SimpleNamespace(positions=as_device(positions), token_seq=torch.zeros(tokens, dtype=torch.int32, device=DEVICE), n_seqs=1, all_single=tokens == 1,
+                           decode_splits=0, max_len=positions[-1] + 1, cu_seqlens=as_device([0, tokens]), seq_start=as_device([positions[0]]),
+                           seq_len=as_device([positions[-1] + 1]))
+    pages = as_device([page_of])
     out = torch.empty((tokens, heads * vdim), dtype=TORCH[dtype], device=DEVICE)
     lam = float(torch.exp((W["m.lq1"].double() * W["m.lk1"].double()).sum()) - torch.exp((W["m.lq2"].double() * W["m.lk2"].double()).sum())) + mixer["diff"]
-    width = heads * 2 * dim + kv_heads * (2 * dim + vdim)
-    kernels.diff_attention(queries, cache_rows, projected[:, width:], out, step, pages, kv_heads, vdim, mixer["scale"], mixer["mask"]["size"], lam, eps, 1.0 - mixer["diff"])
+    gate = projected[:, heads * 2 * dim + kv_heads * (2 * dim + vdim) :]
+    norms = (on_device(W["m.q.norm"]), on_device(W["m.k.norm"]), eps, inv_freq, rotary)
+    if isinstance(cache, tuple):
+        wide = max(dim, vdim)
+        queries = torch.empty((tokens, 2 * heads, wide), dtype=TORCH[dtype], device=DEVICE)
+        kernels.diff_prepare_wide(projected, *norms, queries, cache[0], cache[1], step.positions, step.token_seq, pages, heads, kv_heads, dim, vdim)
+        attended = torch.empty((tokens, 2 * heads * wide), dtype=TORCH[dtype], device=DEVICE)
+        kernels.attention(queries.view(tokens, -1), cache[0], cache[1], attended, step, pages, 2 * heads, 2 * kv_heads, wide, mixer["scale"], mixer["mask"]["size"])
+        kernels.diff_combine(attended.view(tokens, 2 * heads, wide), gate, out, heads, kv_heads, vdim, lam, eps, 1.0 - mixer["diff"])
+    else:
+        queries = torch.empty((tokens, heads, 2, dim), dtype=TORCH[dtype], device=DEVICE)
+        kernels.diff_prepare(projected, *norms, queries, cache, step.positions, step.token_seq, pages, heads, kv_heads, dim, vdim)
+        kernels.diff_attention(queries, cache, gate, out, step, pages, kv_heads, vdim, mixer["scale"], mixer["mask"]["size"], lam, eps, 1.0 - mixer["diff"])
     return out.float().cpu()
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("heads, kv_heads, dim, vdim, window, rot_dims", [(4, 2, 16, 24, 37, 8), (1, 1, 12, 150, 1, 6), (9, 3, 10, 6, 64, 10), (2, 1, 24, 40, 1000, 0)])
+@pytest.mark.parametrize("heads, kv_heads, dim, vdim, window, rot_dims", [(4, 2, 16, 24, 37, 8), (1, 1, 12, 150, 1, 6), (9, 3, 10, 6, 64, 10), (2, 1, 24, 40, 1000, 0),
+                                                                          (4, 2, 16, 32, 37, 8), (2, 1, 64, 128, 100, 32), (3, 3, 48, 16, 64, 48), (8, 1, 32, 64, 1, 2)])
 def test_differential_attention_kernels_over_scattered_pages(dtype, heads, kv_heads, dim, vdim, window, rot_dims):
     """A prompt of 150 tokens, then 60 single tokens, over pages 6, 1, 4, 0 of a pool; against the plain mixer with an identity as
     its output projection."""
@@ -231,22 +254,24 @@ def test_differential_attention_kernels_over_scattered_pages(dtype, heads, kv_he
          "m.lq1": 0.3 * torch.randn(dim), "m.lk1": 0.3 * torch.randn(dim), "m.lq2": 0.3 * torch.randn(dim), "m.lk2": 0.3 * torch.randn(dim)}
     h = torch.randn(total, width)
     wanted = plain.differential_attention(h.double(), {name: value.double() for name, value in W.items()}, "m", mixer, eps)
-    rows = torch.full((8, 64, kv_heads * (2 * dim + vdim)), float("nan"), dtype=TORCH[dtype], device=DEVICE)
+    rows = attention_cache(mixer, 8, dtype, float("nan"))
     page_of = [6, 1, 4, 0]
     found = [run_attention_kernels(h[:150], W, mixer, eps, dtype, list(range(150)), page_of, rows)]
     for position in range(150, total):
         found.append(run_attention_kernels(h[position : position + 1], W, mixer, eps, dtype, [position], page_of, rows))
     assert relative_error(torch.cat(found), wanted) < (2e-5 if dtype == "float32" else 3e-2)
-    assert torch.isnan(rows[[2, 3, 5, 7]].float()).all()                  # nothing was written outside the sequence's pages
+    for pool in rows if isinstance(rows, tuple) else (rows,):
+        assert torch.isnan(pool[[2, 3, 5, 7]].float()).all()              # nothing was written outside the sequence's pages
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_one_key_that_stands_out_is_seen_at_the_window_edge_and_not_beyond(dtype):
+@pytest.mark.parametrize("vdim", [24, 32])      # one row per position; ordinary heads
+def test_one_key_that_stands_out_is_seen_at_the_window_edge_and_not_beyond(dtype, vdim):
     """Queries whose first map points exactly along one key far back: the key sits on the window's last visible position for some
     queries and one position further for others (also across a page border); scores of 64 against a spread of a few make that key
     the whole softmax if it is seen, so a window that is one position off changes the result altogether."""
     torch.manual_seed(9)
-    heads, kv_heads, dim, vdim, window, width, eps, total = 2, 1, 16, 24, 33, 2 * 2 * 16, 1e-5, 200
+    heads, kv_heads, dim, window, width, eps, total = 2, 1, 16, 33, 2 * 2 * 16, 1e-5, 200
     mixer = bm.attention(heads, kv_heads, dim, vdim, window, 0, scale=4.0, diff=0.2)["mixer"]
     # The input is the query itself: W_q is the identity, W_k picks the first head's first map.
     W = {"m.q": torch.eye(heads * 2 * dim, width), "m.k": torch.zeros(kv_heads * 2 * dim, width), "m.v": torch.randn(kv_heads * vdim, width) / 5,
@@ -260,11 +285,11 @@ def test_one_key_that_stands_out_is_seen_at_the_window_edge_and_not_beyond(dtype
     for query in (50, 80, 95, 129, 160, 190):
         h[query, :dim] = h[query - window, :dim]               # just outside
     wanted = plain.differential_attention(h.double(), {name: value.double() for name, value in W.items()}, "m", mixer, eps)
-    rows = torch.zeros((4, 64, kv_heads * (2 * dim + vdim)), dtype=TORCH[dtype], device=DEVICE)
+    rows = attention_cache(mixer, 4, dtype, 0.0)
     whole = run_attention_kernels(h, W, mixer, eps, dtype, list(range(total)), [2, 0, 3, 1], rows)
     # bfloat16 rounds queries and keys: a score of 64 moves by a quarter, its weight with it; a lost or added key moves the result by 0.3 or more
     assert relative_error(whole, wanted) < (2e-5 if dtype == "float32" else 8e-2)
-    rows.zero_()
+    rows = attention_cache(mixer, 4, dtype, 0.0)
     singly = [run_attention_kernels(h[:30], W, mixer, eps, dtype, list(range(30)), [2, 0, 3, 1], rows)]
     singly += [run_attention_kernels(h[p : p + 1], W, mixer, eps, dtype, [p], [2, 0, 3, 1], rows) for p in range(30, total)]
     assert relative_error(torch.cat(singly), wanted) < (2e-5 if dtype == "float32" else 8e-2)
