@@ -15,6 +15,28 @@ namespace {
 
 constexpr int kWarps = 8;
 constexpr int kMaxOwned = 8;      // value columns per lane: vdim <= 256
+constexpr int kMaxPairs = 256;    // rotated pairs whose sine and cosine a block keeps (more are computed where they are used)
+
+// Sine and cosine of position * inv_freq[i] for the block's token, once for all of its maps.
+__device__ __forceinline__ void fill_turns(float2* turns, const float* __restrict__ inv_freq, int rotary, int position) {
+    const int pairs = rotary / 2 < kMaxPairs ? rotary / 2 : kMaxPairs;
+    for (int pair = threadIdx.x; pair < pairs; pair += blockDim.x) {
+        float sine, cosine;
+        sincosf(static_cast<float>(position) * inv_freq[pair], &sine, &cosine);
+        turns[pair] = make_float2(cosine, sine);
+    }
+    __syncthreads();
+}
+
+__device__ __forceinline__ float2 turn_of(const float2* turns, const float* __restrict__ inv_freq, int pair, int position) {
+    if (pair < kMaxPairs) return turns[pair];
+    float sine, cosine;
+    sincosf(static_cast<float>(position) * inv_freq[pair], &sine, &cosine);
+    return make_float2(cosine, sine);
+}
+
+__device__ __forceinline__ void store_two(float* target, float a, float b) { *reinterpret_cast<float2*>(target) = make_float2(a, b); }
+__device__ __forceinline__ void store_two(bf16* target, float a, float b) { *reinterpret_cast<__nv_bfloat162*>(target) = __floats2bfloat162_rn(a, b); }
 
 __device__ __forceinline__ float sigmoid(float z) { return 1.0f / (1.0f + expf(-z)); }
 
@@ -29,6 +51,8 @@ diff_prepare_kernel(const T* __restrict__ projected, long long projected_stride,
     grid_dependency_wait();
     const int token = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int position = positions[token];
+    __shared__ float2 turns[kMaxPairs];
+    fill_turns(turns, inv_freq, rotary, position);
     const int row_width = kv_heads * (2 * dim + vdim);
     const T* source_row = projected + static_cast<size_t>(token) * projected_stride;
     T* row = nullptr;
@@ -54,9 +78,8 @@ diff_prepare_kernel(const T* __restrict__ projected, long long projected_stride,
             float u = to_float(source[first]) * inverse * weight[first];
             float w = second ? to_float(source[first + 1]) * inverse * weight[first + 1] : 0.0f;
             if (first + 1 < rotary) {
-                float sine, cosine;
-                sincosf(static_cast<float>(position) * inv_freq[pair], &sine, &cosine);
-                const float a = u * cosine - w * sine, b = w * cosine + u * sine;
+                const float2 turn = turn_of(turns, inv_freq, pair, position);
+                const float a = u * turn.x - w * turn.y, b = w * turn.x + u * turn.y;
                 u = a; w = b;
             }
             target[first] = from_float<T>(u);
@@ -171,6 +194,8 @@ diff_prepare_wide_kernel(const T* __restrict__ projected, long long projected_st
     grid_dependency_wait();
     const int token = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int position = positions[token];
+    __shared__ float2 turns[kMaxPairs];
+    fill_turns(turns, inv_freq, rotary, position);
     const T* source_row = projected + static_cast<size_t>(token) * projected_stride;
     size_t page_base = 0;
     if (write_cache) {
@@ -202,13 +227,11 @@ diff_prepare_wide_kernel(const T* __restrict__ projected, long long projected_st
             float u = first < dim ? to_float(source[first]) * inverse * weight[first] : 0.0f;
             float w = first + 1 < dim ? to_float(source[first + 1]) * inverse * weight[first + 1] : 0.0f;
             if (first + 1 < rotary) {
-                float sine, cosine;
-                sincosf(static_cast<float>(position) * inv_freq[pair], &sine, &cosine);
-                const float a = u * cosine - w * sine, b = w * cosine + u * sine;
+                const float2 turn = turn_of(turns, inv_freq, pair, position);
+                const float a = u * turn.x - w * turn.y, b = w * turn.x + u * turn.y;
                 u = a; w = b;
             }
-            target[first] = from_float<T>(u);
-            if (first + 1 < wide) target[first + 1] = from_float<T>(w);
+            store_two(target + first, u, w);        // `wide` is even and every head starts on a multiple of it
         }
     }
     if (write_cache) {
@@ -220,34 +243,63 @@ diff_prepare_wide_kernel(const T* __restrict__ projected, long long projected_st
     }
 }
 
-// grid: tokens; a warp per head.  attended [tokens, 2 * heads, wide] in the slots of the kernel above.
-template <typename T>
+// grid: tokens; a warp per head.  attended [tokens, 2 * heads, wide] in the slots of the kernel above.  A lane owns runs of V
+// neighbouring columns (V = 4 where vdim, wide and the gate's rows allow 8-byte accesses).
+template <typename T, int V>
 __global__ void __launch_bounds__(kWarps * 32)
 diff_combine_kernel(const T* __restrict__ attended, const T* __restrict__ gate, long long gate_stride, T* __restrict__ out, int heads, int kv_heads,
                     int vdim, int wide, float lambda, float eps, float post_scale) {
     grid_dependents_launch();
     grid_dependency_wait();
+    constexpr int kRuns = kMaxOwned / V;
     const int token = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, per_group = heads / kv_heads;
     for (int head = warp; head < heads; head += kWarps) {
         const int slot = (head / per_group) * 2 * per_group + head % per_group;
         const T* first = attended + (static_cast<size_t>(token) * 2 * heads + slot) * wide;
         const T* second = first + static_cast<size_t>(per_group) * wide;
-        float held[kMaxOwned];
+        const T* gates = gate ? gate + static_cast<size_t>(token) * gate_stride + head * vdim : nullptr;
+        T* target = out + (static_cast<size_t>(token) * heads + head) * vdim;
+        float held[kRuns][V];
         float squares = 0.0f;
 #pragma unroll
-        for (int i = 0; i < kMaxOwned; ++i) {
-            const int column = lane + 32 * i;
-            held[i] = column < vdim ? to_float(first[column]) - lambda * to_float(second[column]) : 0.0f;
-            squares += held[i] * held[i];
+        for (int i = 0; i < kRuns; ++i) {
+            const int column = (lane + 32 * i) * V;
+            if (column < vdim) {
+                __align__(8) T a[V];
+                __align__(8) T b[V];
+                if constexpr (V == 4) {
+                    *reinterpret_cast<uint2*>(a) = *reinterpret_cast<const uint2*>(first + column);      // V == 4 is used for 2-byte types only
+                    *reinterpret_cast<uint2*>(b) = *reinterpret_cast<const uint2*>(second + column);
+                } else {
+                    a[0] = first[column];
+                    b[0] = second[column];
+                }
+#pragma unroll
+                for (int e = 0; e < V; ++e) {
+                    held[i][e] = to_float(a[e]) - lambda * to_float(b[e]);
+                    squares += held[i][e] * held[i][e];
+                }
+            }
         }
         const float inverse = post_scale / sqrtf(warp_sum(squares) / static_cast<float>(vdim) + eps);
 #pragma unroll
-        for (int i = 0; i < kMaxOwned; ++i) {
-            const int column = lane + 32 * i;
+        for (int i = 0; i < kRuns; ++i) {
+            const int column = (lane + 32 * i) * V;
             if (column < vdim) {
-                float value = held[i] * inverse;
-                if (gate) value *= sigmoid(to_float(gate[static_cast<size_t>(token) * gate_stride + head * vdim + column]));
-                out[(static_cast<size_t>(token) * heads + head) * vdim + column] = from_float<T>(value);
+                __align__(8) T g[V];
+                __align__(8) T result[V];
+                if (gates) {
+                    if constexpr (V == 4) *reinterpret_cast<uint2*>(g) = *reinterpret_cast<const uint2*>(gates + column);
+                    else g[0] = gates[column];
+                }
+#pragma unroll
+                for (int e = 0; e < V; ++e) {
+                    float value = held[i][e] * inverse;
+                    if (gates) value *= sigmoid(to_float(g[e]));
+                    result[e] = from_float<T>(value);
+                }
+                if constexpr (V == 4) *reinterpret_cast<uint2*>(target + column) = *reinterpret_cast<const uint2*>(result);
+                else target[column] = result[0];
             }
         }
     }
@@ -283,14 +335,18 @@ TAU_EXPORT int tau_diff_combine(int dtype, const void* attended, const void* gat
     if (tokens <= 0) return 0;
     if (!attended || !out || heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0 || vdim <= 0 || vdim > 32 * kMaxOwned || wide < vdim) return cudaErrorInvalidValue;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (dtype == TAU_F32)
-        tau_launch(diff_combine_kernel<float>, dim3(tokens), dim3(kWarps * 32), 0, s, static_cast<const float*>(attended), static_cast<const float*>(gate),
+    if (dtype == TAU_F32) {
+        tau_launch(diff_combine_kernel<float, 1>, dim3(tokens), dim3(kWarps * 32), 0, s, static_cast<const float*>(attended), static_cast<const float*>(gate),
                    gate_stride, static_cast<float*>(out), heads, kv_heads, vdim, wide, lambda, eps, post_scale);
-    else if (dtype == TAU_BF16)
-        tau_launch(diff_combine_kernel<bf16>, dim3(tokens), dim3(kWarps * 32), 0, s, static_cast<const bf16*>(attended), static_cast<const bf16*>(gate),
-                   gate_stride, static_cast<bf16*>(out), heads, kv_heads, vdim, wide, lambda, eps, post_scale);
-    else
+    } else if (dtype == TAU_BF16) {
+        const bool four = vdim % 4 == 0 && wide % 4 == 0 && gate_stride % 4 == 0
+                          && ((reinterpret_cast<uintptr_t>(attended) | reinterpret_cast<uintptr_t>(gate) | reinterpret_cast<uintptr_t>(out)) & 7) == 0;
+        tau_launch(four ? diff_combine_kernel<bf16, 4> : diff_combine_kernel<bf16, 1>, dim3(tokens), dim3(kWarps * 32), 0, s,
+                   static_cast<const bf16*>(attended), static_cast<const bf16*>(gate), gate_stride, static_cast<bf16*>(out), heads, kv_heads, vdim, wide,
+                   lambda, eps, post_scale);
+    } else {
         return cudaErrorInvalidValue;
+    }
     return tau_launch_status();
 }
 

@@ -950,16 +950,17 @@ def diff_combine(attended, gate, out, n_heads: int, n_kv_heads: int, vdim: int, 
 
 # ---------------------------------------------------------------------------- sublayer arrangement on a 32-bit stream
 def causal_taps(stream, weight, state, step, read_out, plain_out=None, update: bool = True) -> None:
-    """`read_out[t] = stream[t] + sum_j weight[:, j] * stream[t - taps + 1 + j]` over each sequence's run of the step, the rows before
+    """`read_out[t] = stream[t] + sum_j weight[j] * stream[t - taps + 1 + j]` (`weight` float32 [taps, width]: tap by tap, so that a
+    tap's channels lie side by side) over each sequence's run of the step, the rows before
     the run's first token taken from `state[slot]` ([slots, taps - 1, width] float32: the sequence's last inputs, zeros at its start);
     `plain_out` (optional) receives `stream` itself in the output's dtype.  With `update` the state then becomes the last `taps - 1`
     inputs of each sequence (a second launch, or the same one where every sequence brings one token)."""
     _on_device(stream, weight, state, read_out, plain_out)
     tokens, width = stream.shape
-    taps = 0 if weight is None else weight.shape[1]      # without a weight the outputs are the stream itself, rounded
+    taps = 0 if weight is None else weight.shape[0]      # without a weight the outputs are the stream itself, rounded
     _require(stream.dtype == torch.float32 and stream.is_contiguous(), "the stream must be contiguous float32")
     if weight is not None:
-        _require(weight.dtype == torch.float32 and weight.shape == (width, taps) and weight.is_contiguous() and taps >= 1, "the taps must be float32 [width, taps]")
+        _require(weight.dtype == torch.float32 and weight.shape == (taps, width) and weight.is_contiguous() and taps >= 1, "the taps must be float32 [taps, width]")
     if taps > 1:
         _require(state is not None and state.dtype == torch.float32 and state.shape[1:] == (taps - 1, width) and state.is_contiguous(),
                  "the state must be float32 [slots, taps - 1, width]")

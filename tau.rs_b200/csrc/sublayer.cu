@@ -1,7 +1,7 @@
 // Kernels of a block arrangement that normalises what a sublayer returns instead of what it reads, on a residual stream kept
 // in 32-bit:
 //
-//   causal taps     read[t] = x[t] + sum_j w[:, j] * x[t - taps + 1 + j], a short causal convolution over time on each channel whose
+//   causal taps     read[t] = x[t] + sum_j w[j, :] * x[t - taps + 1 + j], a short causal convolution over time on each channel whose
 //                   rows before a run's first token come from the sequence's state (its last taps - 1 inputs; zeros at the start)
 //   taps state      the state after the run: the last taps - 1 inputs of the sequence
 //   gated add norm  target = source + norm(branch * sigmoid(gate)) * weight + bias, the norm centred (layer norm) or not (RMS)
@@ -86,8 +86,9 @@ causal_taps_kernel(const float* __restrict__ x, const float* __restrict__ weight
             const int source = local - (taps - 1) + j;
             const Pack<V> value = source >= 0 ? load_pack<V>(x, TAU_F32, static_cast<size_t>(first + source) * width + column)
                                               : load_pack<V>(kept, TAU_F32, static_cast<size_t>(taps - 1 + source) * width + column);
+            const Pack<V> tap = load_pack<V>(weight, TAU_F32, static_cast<size_t>(j) * width + column);      // weight [taps, width]
 #pragma unroll
-            for (int e = 0; e < V; ++e) sum.v[e] = fmaf(weight[static_cast<size_t>(column + e) * taps + j], value.v[e], sum.v[e]);
+            for (int e = 0; e < V; ++e) sum.v[e] = fmaf(tap.v[e], value.v[e], sum.v[e]);
         }
 #pragma unroll
         for (int e = 0; e < V; ++e) sum.v[e] += own.v[e];
@@ -266,15 +267,27 @@ norm_rows_kernel(const void* __restrict__ values, int values_code, const int* __
     }
 }
 
-template <typename T>
+// A thread takes 16 bytes (V elements) where the tensors allow it.
+template <typename T, int V>
 __global__ void __launch_bounds__(kThreads)
 relu_squared_kernel(const T* z, T* out, long long count) {
     grid_dependents_launch();
     grid_dependency_wait();
-    const long long index = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    const long long index = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) * V;
     if (index >= count) return;
-    const float value = fmaxf(to_float(z[index]), 0.0f);
-    out[index] = from_float<T>(value * value);
+    if constexpr (V == 1) {
+        const float value = fmaxf(to_float(z[index]), 0.0f);
+        out[index] = from_float<T>(value * value);
+    } else {
+        uint4 raw = *reinterpret_cast<const uint4*>(z + index);
+        T* values = reinterpret_cast<T*>(&raw);
+#pragma unroll
+        for (int e = 0; e < V; ++e) {
+            const float value = fmaxf(to_float(values[e]), 0.0f);
+            values[e] = from_float<T>(value * value);
+        }
+        *reinterpret_cast<uint4*>(out + index) = raw;
+    }
 }
 
 // Whether every pointer given (null ones aside) lies on a 16-byte boundary.
@@ -298,7 +311,7 @@ TAU_EXPORT int tau_causal_taps(int dtype, const float* x, const float* weight, f
     if (!x || (!weight && taps > 0) || (!state && taps > 1) || !token_seq || !cu_seqlens || !seq_slot || !read_out || sequences <= 0 || width <= 0 || taps < 0) return cudaErrorInvalidValue;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const int shift = (update && taps > 1 && all_single && tokens == sequences) ? 1 : 0;
-    const bool wide = width % 4 == 0 && aligned16(x, state, read_out, plain_out);
+    const bool wide = width % 4 == 0 && aligned16(x, weight, state, read_out, plain_out);
     if (dtype == TAU_F32) {
         auto kernel = wide ? causal_taps_kernel<float, 4> : causal_taps_kernel<float, 1>;
         tau_launch(kernel, dim3(tokens), dim3(kThreads), 0, s, x, weight, state, token_seq, cu_seqlens, seq_slot,
@@ -404,9 +417,11 @@ TAU_EXPORT int tau_relu_squared(int dtype, const void* z, void* out, long long c
     if (count <= 0) return 0;
     if (!z || !out) return cudaErrorInvalidValue;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    const dim3 grid(static_cast<unsigned>((count + kThreads - 1) / kThreads));
-    if (dtype == TAU_F32) tau_launch(relu_squared_kernel<float>, grid, dim3(kThreads), 0, s, static_cast<const float*>(z), static_cast<float*>(out), count);
-    else if (dtype == TAU_BF16) tau_launch(relu_squared_kernel<bf16>, grid, dim3(kThreads), 0, s, static_cast<const bf16*>(z), static_cast<bf16*>(out), count);
+    const bool wide = count % 8 == 0 && aligned16(z, out);
+    const int per_thread = !wide ? 1 : dtype == TAU_BF16 ? 8 : 4;
+    const dim3 grid(static_cast<unsigned>((count / per_thread + kThreads - 1) / kThreads));
+    if (dtype == TAU_F32) tau_launch(wide ? relu_squared_kernel<float, 4> : relu_squared_kernel<float, 1>, grid, dim3(kThreads), 0, s, static_cast<const float*>(z), static_cast<float*>(out), count);
+    else if (dtype == TAU_BF16) tau_launch(wide ? relu_squared_kernel<bf16, 8> : relu_squared_kernel<bf16, 1>, grid, dim3(kThreads), 0, s, static_cast<const bf16*>(z), static_cast<bf16*>(out), count);
     else return cudaErrorInvalidValue;
     return tau_launch_status();
 }

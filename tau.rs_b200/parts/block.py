@@ -212,7 +212,8 @@ class SublayerNormBlock(Block):
         prefix, spec = self.spec.prefix, self.spec
         for part in self._children:
             part.finalize_weights()
-        self.taps = self._held.pop(f"{prefix}.{self.taps_name}") if spec.input_taps else None
+        # Stored [width, taps]; the kernel reads tap by tap, a tap's channels side by side.
+        self.taps = self._held.pop(f"{prefix}.{self.taps_name}").t().contiguous() if spec.input_taps else None
         self.mix = self._held.pop(f"{prefix}.{self.mix_name}") if spec.depth_mix else None
         self.side_norm = self._held.pop(f"{prefix}.{self.side_name}.norm") if spec.token_side is not None else None
 

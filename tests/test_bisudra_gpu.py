@@ -95,7 +95,7 @@ def test_causal_taps_carry_their_tail_from_step_to_step(dtype, taps):
         x = on_device(torch.cat(new))
         read = torch.empty(x.shape, dtype=TORCH[dtype], device=DEVICE)
         rounded = torch.empty_like(read)
-        kernels.causal_taps(x, on_device(weight), state, packed_step(runs, slots), read, rounded)
+        kernels.causal_taps(x, on_device(weight.T), state, packed_step(runs, slots), read, rounded)      # the kernel wants [taps, width]
         wanted = []
         for index, rows in enumerate(new):
             history[index] = torch.cat([history[index], rows])
