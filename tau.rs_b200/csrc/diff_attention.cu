@@ -190,12 +190,16 @@ diff_prepare_wide_kernel(const T* __restrict__ projected, long long projected_st
                          T* __restrict__ value_pages, const int* __restrict__ positions, const int* __restrict__ token_seq,
                          const int* __restrict__ page_rows, int page_stride, int page_tokens, int heads, int kv_heads, int dim, int vdim, int wide,
                          int write_cache) {
+    // grid: (tokens, y); the warps of a token's y blocks share out its items: the query maps, then (with `write_cache`) the key
+    // maps, then the value heads.  Few tokens get a warp per item, many tokens one block each.
     grid_dependents_launch();
     grid_dependency_wait();
     const int token = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int position = positions[token];
     __shared__ float2 turns[kMaxPairs];
     fill_turns(turns, inv_freq, rotary, position);
+    const int q_maps = heads * 2, maps = q_maps + (write_cache ? kv_heads * 2 : 0), items = maps + (write_cache ? kv_heads * 2 : 0);
+    const int per_group = heads / kv_heads;
     const T* source_row = projected + static_cast<size_t>(token) * projected_stride;
     size_t page_base = 0;
     if (write_cache) {
@@ -203,8 +207,16 @@ diff_prepare_wide_kernel(const T* __restrict__ projected, long long projected_st
         page_base = static_cast<size_t>(page) * 2 * kv_heads * page_tokens * wide + static_cast<size_t>(position % page_tokens) * wide;
     }
     const size_t head_pitch = static_cast<size_t>(page_tokens) * wide;
-    const int q_maps = heads * 2, maps = q_maps + (write_cache ? kv_heads * 2 : 0), per_group = heads / kv_heads;
-    for (int map = warp; map < maps; map += kWarps) {
+    for (int item = blockIdx.y * kWarps + warp; item < items; item += gridDim.y * kWarps) {
+        if (item >= maps) {          // a value head: the group's values, zeros behind them
+            const int head = item - maps;
+            const T* values = source_row + static_cast<size_t>(q_maps + kv_heads * 2) * dim + static_cast<size_t>(head >> 1) * vdim;
+            T* target = value_pages + page_base + static_cast<size_t>(head) * head_pitch;
+            for (int column = 2 * lane; column < wide; column += 64)
+                store_two(target + column, column < vdim ? to_float(values[column]) : 0.0f, column + 1 < vdim ? to_float(values[column + 1]) : 0.0f);
+            continue;
+        }
+        const int map = item;
         const bool is_query = map < q_maps;
         const T* source = source_row + static_cast<size_t>(map) * dim;
         T* target;
@@ -232,13 +244,6 @@ diff_prepare_wide_kernel(const T* __restrict__ projected, long long projected_st
                 u = a; w = b;
             }
             store_two(target + first, u, w);        // `wide` is even and every head starts on a multiple of it
-        }
-    }
-    if (write_cache) {
-        const T* values = source_row + static_cast<size_t>(q_maps + kv_heads * 2) * dim;
-        for (int item = threadIdx.x; item < kv_heads * 2 * wide; item += blockDim.x) {
-            const int head = item / wide, column = item % wide;
-            value_pages[page_base + static_cast<size_t>(head) * head_pitch + column] = column < vdim ? values[(head >> 1) * vdim + column] : from_float<T>(0.0f);
         }
     }
 }
@@ -317,12 +322,14 @@ TAU_EXPORT int tau_diff_prepare_wide(int dtype, const void* projected, long long
         || (write_cache && (!key_pages || !value_pages || !token_seq || !page_rows)))
         return cudaErrorInvalidValue;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int items = heads * 2 + (write_cache ? kv_heads * 4 : 0);
+    const dim3 grid(tokens, tokens >= 1024 ? 1 : (items + kWarps - 1) / kWarps);
     if (dtype == TAU_F32)
-        tau_launch(diff_prepare_wide_kernel<float>, dim3(tokens), dim3(kWarps * 32), 0, s, static_cast<const float*>(projected), projected_stride, q_weight,
+        tau_launch(diff_prepare_wide_kernel<float>, grid, dim3(kWarps * 32), 0, s, static_cast<const float*>(projected), projected_stride, q_weight,
                    k_weight, eps, inv_freq, rotary, static_cast<float*>(queries), static_cast<float*>(key_pages), static_cast<float*>(value_pages), positions,
                    token_seq, page_rows, page_stride, page_tokens, heads, kv_heads, dim, vdim, wide, write_cache);
     else if (dtype == TAU_BF16)
-        tau_launch(diff_prepare_wide_kernel<bf16>, dim3(tokens), dim3(kWarps * 32), 0, s, static_cast<const bf16*>(projected), projected_stride, q_weight,
+        tau_launch(diff_prepare_wide_kernel<bf16>, grid, dim3(kWarps * 32), 0, s, static_cast<const bf16*>(projected), projected_stride, q_weight,
                    k_weight, eps, inv_freq, rotary, static_cast<bf16*>(queries), static_cast<bf16*>(key_pages), static_cast<bf16*>(value_pages), positions,
                    token_seq, page_rows, page_stride, page_tokens, heads, kv_heads, dim, vdim, wide, write_cache);
     else

@@ -241,7 +241,7 @@ def run_attention_kernels(h, W, mixer, eps, dtype, positions, page_of, cache):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("heads, kv_heads, dim, vdim, window, rot_dims", [(4, 2, 16, 24, 37, 8), (1, 1, 12, 150, 1, 6), (9, 3, 10, 6, 64, 10), (2, 1, 24, 40, 1000, 0),
-                                                                          (4, 2, 16, 32, 37, 8), (2, 1, 64, 128, 100, 32), (3, 3, 48, 16, 64, 48), (8, 1, 32, 64, 1, 2)])
+                                                                          (4, 2, 16, 32, 37, 8), (2, 1, 64, 128, 100, 32), (3, 3, 48, 16, 64, 48), (8, 1, 32, 64, 1, 2), (2, 1, 32, 160, 50, 32)])
 def test_differential_attention_kernels_over_scattered_pages(dtype, heads, kv_heads, dim, vdim, window, rot_dims):
     """A prompt of 150 tokens, then 60 single tokens, over pages 6, 1, 4, 0 of a pool; against the plain mixer with an identity as
     its output projection."""
