@@ -102,7 +102,7 @@ causal_taps_kernel(const float* __restrict__ x, const float* __restrict__ weight
     }
 }
 
-// grid: sequences.  Runs after every reader of the old state in stream order.  A thread owns a channel and walks the rows upwards:
+// grid: (sequences, ceil(width / threads)).  Runs after every reader of the old state in stream order.  A thread owns a channel and walks the rows upwards:
 // row i takes the input at run-local index count - (taps - 1) + i, which for a negative index is the old row i + count, not yet overwritten.
 __global__ void __launch_bounds__(kThreads)
 taps_state_kernel(const float* __restrict__ x, float* __restrict__ state, const int* __restrict__ cu_seqlens, const int* __restrict__ seq_slot,
@@ -111,7 +111,8 @@ taps_state_kernel(const float* __restrict__ x, float* __restrict__ state, const 
     grid_dependency_wait();
     const int seq = blockIdx.x, first = cu_seqlens[seq], count = cu_seqlens[seq + 1] - first;
     float* kept = state + static_cast<size_t>(seq_slot[seq]) * (taps - 1) * width;
-    for (int column = threadIdx.x; column < width; column += blockDim.x) {
+    const int column = blockIdx.y * blockDim.x + threadIdx.x;
+    if (column < width) {
         for (int i = 0; i < taps - 1; ++i) {
             const int source = count - (taps - 1) + i;
             kept[static_cast<size_t>(i) * width + column] = source >= 0 ? x[static_cast<size_t>(first + source) * width + column]
@@ -325,7 +326,7 @@ TAU_EXPORT int tau_causal_taps(int dtype, const float* x, const float* weight, f
     }
     int status = tau_launch_status();
     if (status != 0 || !update || taps < 2 || shift) return status;
-    tau_launch(taps_state_kernel, dim3(sequences), dim3(kThreads), 0, s, x, state, cu_seqlens, seq_slot, width, taps);
+    tau_launch(taps_state_kernel, dim3(sequences, (width + kThreads - 1) / kThreads), dim3(kThreads), 0, s, x, state, cu_seqlens, seq_slot, width, taps);
     return tau_launch_status();
 }
 
