@@ -14,7 +14,7 @@
 namespace {
 
 constexpr int kWarps = 8;
-constexpr int kMaxOwned = 8;      // value columns per lane: vdim <= 256
+constexpr int kMaxOwned = 16;     // value columns per lane: vdim <= 512
 constexpr int kMaxPairs = 256;    // rotated pairs whose sine and cosine a block keeps (more are computed where they are used)
 
 // Sine and cosine of position * inv_freq[i] for the block's token, once for all of its maps.

@@ -841,7 +841,7 @@ def latent_attention(queries, rows, out, sinks, positions, token_seq, page_rows,
 
 
 # ---------------------------------------------------------------------------- differential attention
-DIFF_MAX_VALUE_DIM = 256
+DIFF_MAX_VALUE_DIM = 512
 
 
 def diff_prepare(projected, q_weight, k_weight, eps: float, inv_freq, rotary_dim: int, queries, rows, positions, token_seq, page_rows,

@@ -197,10 +197,10 @@ def test_a_router_with_a_bias_weighs_by_the_softmax_of_the_chosen_logits(experts
 
 def attention_cache(mixer, pages, dtype, fill):
     """Pages for one layer in the layout that the sizes choose: keys and values of ordinary heads where max(dim, vdim) is a multiple
-    of 16, else one row per position."""
+    of 16 up to 256, else one row per position."""
     kv_heads, dim, vdim = mixer["kv_heads"], mixer["dim"], mixer["vdim"]
     wide = max(dim, vdim)
-    if wide % 16 == 0:
+    if wide % 16 == 0 and wide <= 256:
         return tuple(torch.full((pages, 2 * kv_heads, 64, wide), fill, dtype=TORCH[dtype], device=DEVICE) for _ in range(2))
     return torch.full((pages, 64, kv_heads * (2 * dim + vdim)), fill, dtype=TORCH[dtype], device=DEVICE)
 
@@ -241,7 +241,7 @@ def run_attention_kernels(h, W, mixer, eps, dtype, positions, page_of, cache):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("heads, kv_heads, dim, vdim, window, rot_dims", [(4, 2, 16, 24, 37, 8), (1, 1, 12, 150, 1, 6), (9, 3, 10, 6, 64, 10), (2, 1, 24, 40, 1000, 0),
-                                                                          (4, 2, 16, 32, 37, 8), (2, 1, 64, 128, 100, 32), (3, 3, 48, 16, 64, 48), (8, 1, 32, 64, 1, 2), (2, 1, 32, 160, 50, 32)])
+                                                                          (4, 2, 16, 32, 37, 8), (2, 1, 64, 128, 100, 32), (3, 3, 48, 16, 64, 48), (8, 1, 32, 64, 1, 2), (2, 1, 32, 160, 50, 32), (1, 1, 16, 320, 40, 4)])
 def test_differential_attention_kernels_over_scattered_pages(dtype, heads, kv_heads, dim, vdim, window, rot_dims):
     """A prompt of 150 tokens, then 60 single tokens, over pages 6, 1, 4, 0 of a pool; against the plain mixer with an identity as
     its output projection."""
